@@ -156,6 +156,34 @@ class PowerSGD(Aggregator):
         sent = (self._powersgd.compressed_num_floats if self._powersgd.params else 0.0) + plain
         return sum(self._all_numels) / max(sent, 1e-30)
 
+    # -- fused optimizer step (native back end + torch.optim.SGD) ------------------------
+    def supports_fused_step(self, optimizer: torch.optim.Optimizer) -> bool:
+        if type(optimizer) is not torch.optim.SGD:
+            return False
+        if _pick_backend(self._backend_request, self.device) != "native":
+            return False
+        for group in optimizer.param_groups:
+            if group.get("maximize", False) or group.get("differentiable", False):
+                return False
+            seen = [("momentum_buffer" in optimizer.state.get(p, {})) and optimizer.state[p]["momentum_buffer"] is not None
+                    for p in group["params"]]
+            if any(seen) and not all(seen):
+                return False
+            for p in group["params"]:
+                if p.dtype != torch.float32 or p.grad is None or not p.is_contiguous() or not p.grad.is_contiguous():
+                    return False
+        return True
+
+    def fused_step(self, optimizer: torch.optim.Optimizer, prepared: bool = False) -> None:
+        """Aggregate and apply SGD inside the native kernels: the averaged gradient is never
+        written to memory. Numerically the same update as `optimizer_step` with
+        `torch.optim.SGD` (weight decay, momentum, dampening, nesterov)."""
+        from .cuda_path import FusedSGDDriver
+
+        if getattr(self, "_fused", None) is None:
+            self._fused = FusedSGDDriver(self)
+        self._fused.step(optimizer, prepared=prepared)
+
     def state_dict(self, gradients: Optional[Sequence[torch.Tensor]] = None) -> Dict:
         from .state import aggregator_state_dict
 

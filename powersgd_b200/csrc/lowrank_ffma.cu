@@ -1,0 +1,350 @@
+// Grouped tall-skinny products on the CUDA cores (exact float32 FMA path).
+//
+//   NT:  Q[m, r] = M^T[m, n] * Phat[n, r]  -  sum_i R_i[m, r] * C_i[r, r]
+//   NN:  P[n, r] = M  [n, m] * Qhat[m, r]  -  sum_i L_i[n, r] * C_i[r, r]
+//
+// One launch covers EVERY compressed matrix of EVERY shape group: the grid walks a tile list
+// built once by the host planner. This replaces the reference's per-group `torch.bmm` and the
+// first `baddbmm_` (powersgd/powersgd.py:185-202): the deflation M <- M - P Q^T is never
+// materialised between half-iterations; the small terms C_i (from the orthonormalisation
+// launch) correct the product instead.
+//
+// At rank r the product does 2r flops per 4 bytes of M, so for r <= 8 float32 FMAs keep up
+// with HBM and this path is bandwidth-bound; it is also the path for matrices whose row
+// pitch is not a multiple of 16 bytes (27, 650 floats), which TMA cannot address.
+//
+// Tiles that cover the same output rows (NT: row blocks of one column block; NN: column
+// blocks of one row block) write partial sums to a scratch arena; the tile that arrives last
+// (arrival counter) adds them in a fixed order, so the result does not depend on scheduling.
+#include "psgd_common.cuh"
+
+constexpr int GEMM_THREADS = 256;
+constexpr int GEMM_WARPS = GEMM_THREADS / 32;
+constexpr int NT_TILE_COLS = 128;   // columns of M per NT tile
+constexpr int NT_MAX_ROWS = 256;    // rows of M per NT tile (P-hat block staged in smem); 128 at RT = 32
+constexpr int NN_CHUNK_COLS = 128;  // columns consumed per inner iteration of an NN tile
+
+struct GemmArgs {
+  const PsgdMat* mats;
+  const PsgdTile* tiles;
+  const float* in;    // orthonormal factor: P-shaped for NT, Q-shaped for NN
+  float* out;         // fresh local factor: Q-shaped for NT, P-shaped for NN
+  int ncorr;
+  const float* corr_fac[PSGD_MAX_HIST];  // earlier local factors on the OUTPUT side
+  const float* corr_c[PSGD_MAX_HIST];    // [mat][r*r] cross products
+  float* partial;     // scratch for split tiles
+  int* tickets;       // arrival counters (all zero between launches)
+};
+
+template <int RT>
+__host__ __device__ constexpr int nt_max_rows() { return RT <= 16 ? NT_MAX_ROWS : NT_MAX_ROWS / 2; }
+
+// ------------------------------------------------------------------------------------------
+// NT: each lane owns 4 columns, each warp strides over the tile's rows.
+// ------------------------------------------------------------------------------------------
+template <int RT, int VEC>
+__global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) {
+  const PsgdTile t = a.tiles[blockIdx.x];
+  const PsgdMat mt = a.mats[t.mat];
+  const int r = mt.r, m = mt.m;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  extern __shared__ float smem[];
+  float* sP = smem;                        // [rows][RT]
+  float* sSum = smem + nt_max_rows<RT>() * RT;   // [128][RT]
+  __shared__ int sLast;
+
+  // stage the tile's rows of P-hat (zero padded to RT columns)
+  const float* __restrict__ pin = a.in + mt.p_off + (long long)t.row0 * r;
+  for (int e = tid; e < t.rows * RT; e += GEMM_THREADS) {
+    const int row = e / RT, k = e % RT;
+    sP[e] = (k < r) ? pin[row * r + k] : 0.f;
+  }
+  __syncthreads();
+
+  float acc[4][RT];
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int k = 0; k < RT; ++k) acc[c][k] = 0.f;
+
+  const float* __restrict__ M = mt.grad;
+  int colv[4];
+  bool colok[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    colv[c] = t.col0 + (VEC == 4 ? 4 * lane + c : lane + 32 * c);
+    colok[c] = colv[c] < t.col0 + t.cols;
+  }
+
+  for (int i0 = warp; i0 < t.rows; i0 += GEMM_WARPS * 4) {
+    float v[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * GEMM_WARPS;
+      const bool rok = i < t.rows;
+      const float* rowp = M + (long long)(t.row0 + (rok ? i : 0)) * m;
+      if (VEC == 4) {
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (rok && colok[0]) q = __ldg(reinterpret_cast<const float4*>(rowp + colv[0]));
+        v[u][0] = q.x; v[u][1] = q.y; v[u][2] = q.z; v[u][3] = q.w;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[u][c] = (rok && colok[c]) ? __ldg(rowp + colv[c]) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * GEMM_WARPS;
+      if (i < t.rows) {
+        const float* pr = sP + i * RT;
+#pragma unroll
+        for (int k = 0; k < RT; ++k) {
+          const float pk = pr[k];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[c][k] = fmaf(v[u][c], pk, acc[c][k]);
+        }
+      }
+    }
+  }
+
+  // deterministic cross-warp sum: warps add in index order
+  for (int w = 0; w < GEMM_WARPS; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int lc = (VEC == 4 ? 4 * lane + c : lane + 32 * c);
+#pragma unroll
+        for (int k = 0; k < RT; ++k) {
+          if (w == 0) sSum[lc * RT + k] = acc[c][k];
+          else sSum[lc * RT + k] += acc[c][k];
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  const int tile_elems = NT_TILE_COLS * RT;
+  if (t.nsplit > 1) {
+    float* mine = a.partial + (long long)(t.slot0 + t.split) * tile_elems;
+    for (int e = tid; e < tile_elems; e += GEMM_THREADS) __stcg(mine + e, sSum[e]);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) sLast = (psgd_atom_add_acqrel_gpu(a.tickets + t.ticket, 1) == t.nsplit - 1);
+    __syncthreads();
+    if (!sLast) return;
+    __threadfence();
+    for (int e = tid; e < tile_elems; e += GEMM_THREADS) {
+      float s = 0.f;
+      for (int p = 0; p < t.nsplit; ++p) s += __ldcg(a.partial + (long long)(t.slot0 + p) * tile_elems + e);
+      sSum[e] = s;
+    }
+    if (tid == 0) a.tickets[t.ticket] = 0;  // ready for the next launch
+    __syncthreads();
+  }
+
+  // epilogue: subtract the deflation terms and store Q rows
+  float* __restrict__ qout = a.out + mt.q_off;
+  for (int e = tid; e < t.cols * r; e += GEMM_THREADS) {
+    const int lc = e / r, k = e % r;
+    const int col = t.col0 + lc;
+    float s = sSum[lc * RT + k];
+    for (int i = 0; i < a.ncorr; ++i) {
+      const float* f = a.corr_fac[i] + mt.q_off + (long long)col * r;
+      const float* cm = a.corr_c[i] + (long long)mt.index * PSGD_CMAT_STRIDE;
+      float d = 0.f;
+      for (int l = 0; l < r; ++l) d = fmaf(f[l], cm[l * r + k], d);
+      s -= d;
+    }
+    qout[(long long)col * r + k] = s;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// NN: each warp owns RPW rows; lanes stride across the columns and shuffle-reduce at the end.
+// ------------------------------------------------------------------------------------------
+template <int RT, int VEC, int RPW>
+__global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nn_kernel(GemmArgs a) {
+  const PsgdTile t = a.tiles[blockIdx.x];
+  const PsgdMat mt = a.mats[t.mat];
+  const int r = mt.r, m = mt.m;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int TILE_ROWS = GEMM_WARPS * RPW;
+
+  __shared__ float sSum[TILE_ROWS * RT];
+  __shared__ int sLast;
+
+  const float* __restrict__ M = mt.grad;
+  const float* __restrict__ qin = a.in + mt.q_off;
+
+  float acc[RPW][RT];
+#pragma unroll
+  for (int u = 0; u < RPW; ++u)
+#pragma unroll
+    for (int k = 0; k < RT; ++k) acc[u][k] = 0.f;
+
+  const int rbase = warp * RPW;
+  const float* rowp[RPW];
+  bool rok[RPW];
+#pragma unroll
+  for (int u = 0; u < RPW; ++u) {
+    rok[u] = rbase + u < t.rows;
+    rowp[u] = M + (long long)(t.row0 + (rok[u] ? rbase + u : 0)) * m;
+  }
+
+  const int cend = t.col0 + t.cols;
+  for (int c0 = t.col0; c0 < cend; c0 += NN_CHUNK_COLS) {
+    int colv[4];
+    bool colok[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      colv[c] = c0 + (VEC == 4 ? 4 * lane + c : lane + 32 * c);
+      colok[c] = colv[c] < cend;
+    }
+    float v[RPW][4];
+#pragma unroll
+    for (int u = 0; u < RPW; ++u) {
+      if (VEC == 4) {
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (rok[u] && colok[0]) q = __ldg(reinterpret_cast<const float4*>(rowp[u] + colv[0]));
+        v[u][0] = q.x; v[u][1] = q.y; v[u][2] = q.z; v[u][3] = q.w;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[u][c] = (rok[u] && colok[c]) ? __ldg(rowp[u] + colv[c]) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      if (colok[c]) {
+        const float* qr = qin + (long long)colv[c] * r;
+#pragma unroll
+        for (int k = 0; k < RT; ++k) {
+          const float qk = (k < r) ? __ldg(qr + k) : 0.f;
+#pragma unroll
+          for (int u = 0; u < RPW; ++u) acc[u][k] = fmaf(v[u][c], qk, acc[u][k]);
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int u = 0; u < RPW; ++u)
+#pragma unroll
+    for (int k = 0; k < RT; ++k) {
+      const float s = psgd_warp_sum(acc[u][k]);
+      if (lane == 0) sSum[(rbase + u) * RT + k] = s;
+    }
+  __syncthreads();
+
+  constexpr int tile_elems = TILE_ROWS * RT;
+  if (t.nsplit > 1) {
+    float* mine = a.partial + (long long)(t.slot0 + t.split) * tile_elems;
+    for (int e = tid; e < tile_elems; e += GEMM_THREADS) __stcg(mine + e, sSum[e]);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) sLast = (psgd_atom_add_acqrel_gpu(a.tickets + t.ticket, 1) == t.nsplit - 1);
+    __syncthreads();
+    if (!sLast) return;
+    __threadfence();
+    for (int e = tid; e < tile_elems; e += GEMM_THREADS) {
+      float s = 0.f;
+      for (int p = 0; p < t.nsplit; ++p) s += __ldcg(a.partial + (long long)(t.slot0 + p) * tile_elems + e);
+      sSum[e] = s;
+    }
+    if (tid == 0) a.tickets[t.ticket] = 0;
+    __syncthreads();
+  }
+
+  float* __restrict__ pout = a.out + mt.p_off;
+  for (int e = tid; e < t.rows * r; e += GEMM_THREADS) {
+    const int lr = e / r, k = e % r;
+    const int row = t.row0 + lr;
+    float s = sSum[lr * RT + k];
+    for (int i = 0; i < a.ncorr; ++i) {
+      const float* f = a.corr_fac[i] + mt.p_off + (long long)row * r;
+      const float* cm = a.corr_c[i] + (long long)mt.index * PSGD_CMAT_STRIDE;
+      float d = 0.f;
+      for (int l = 0; l < r; ++l) d = fmaf(f[l], cm[l * r + k], d);
+      s -= d;
+    }
+    pout[(long long)row * r + k] = s;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host launchers
+// ------------------------------------------------------------------------------------------
+static void fill_args(GemmArgs& a, const void* mats, const void* tiles, const float* in, float* out, int ncorr,
+                      const float* const* corr_fac, const float* const* corr_c, float* partial, int* tickets) {
+  a.mats = (const PsgdMat*)mats;
+  a.tiles = (const PsgdTile*)tiles;
+  a.in = in;
+  a.out = out;
+  a.ncorr = ncorr;
+  for (int i = 0; i < PSGD_MAX_HIST; ++i) {
+    a.corr_fac[i] = i < ncorr ? corr_fac[i] : nullptr;
+    a.corr_c[i] = i < ncorr ? corr_c[i] : nullptr;
+  }
+  a.partial = partial;
+  a.tickets = tickets;
+}
+
+template <int RT, int VEC>
+static int launch_nt(const GemmArgs& a, int ntiles, cudaStream_t stream) {
+  const size_t smem = (size_t)(nt_max_rows<RT>() * RT + NT_TILE_COLS * RT) * sizeof(float);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    PSGD_CUDA_OK(cudaFuncSetAttribute(psgd_gemm_nt_kernel<RT, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
+    configured = true;
+  }
+  psgd_gemm_nt_kernel<RT, VEC><<<ntiles, GEMM_THREADS, smem, stream>>>(a);
+  PSGD_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+template <int RT, int VEC>
+static int launch_nn(const GemmArgs& a, int ntiles, cudaStream_t stream) {
+  constexpr int RPW = RT <= 8 ? 4 : (RT == 16 ? 2 : 1);
+  psgd_gemm_nn_kernel<RT, VEC, RPW><<<ntiles, GEMM_THREADS, 0, stream>>>(a);
+  PSGD_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+#define PSGD_DISPATCH_RT(FN, VECV)                                   \
+  if (max_r <= 1) return FN<1, VECV>(a, ntiles, stream);             \
+  if (max_r <= 2) return FN<2, VECV>(a, ntiles, stream);             \
+  if (max_r <= 4) return FN<4, VECV>(a, ntiles, stream);             \
+  if (max_r <= 8) return FN<8, VECV>(a, ntiles, stream);             \
+  if (max_r <= 16) return FN<16, VECV>(a, ntiles, stream);           \
+  return FN<32, VECV>(a, ntiles, stream);
+
+// Rows handled by one NN tile for the template rank that `max_r` selects (the planner needs it).
+PSGD_API int psgd_gemm_nn_tile_rows(int max_r) {
+  const int rt = max_r <= 1 ? 1 : max_r <= 2 ? 2 : max_r <= 4 ? 4 : max_r <= 8 ? 8 : max_r <= 16 ? 16 : 32;
+  return GEMM_WARPS * (rt <= 8 ? 4 : (rt == 16 ? 2 : 1));
+}
+PSGD_API int psgd_gemm_nt_max_rows(int max_r) { return max_r <= 16 ? NT_MAX_ROWS : NT_MAX_ROWS / 2; }
+PSGD_API int psgd_gemm_template_rank(int max_r) {
+  return max_r <= 1 ? 1 : max_r <= 2 ? 2 : max_r <= 4 ? 4 : max_r <= 8 ? 8 : max_r <= 16 ? 16 : 32;
+}
+
+// `transposed` != 0: NT (Q = M^T P); else NN (P = M Q). `vec4` != 0 only if every matrix of the
+// tile list has a 16-byte aligned base and m % 4 == 0.
+PSGD_API int psgd_gemm_ffma_launch(int transposed, int vec4, int max_r, const void* mats, const void* tiles,
+                                   int ntiles, const float* in, float* out, int ncorr,
+                                   const float* const* corr_fac, const float* const* corr_c, float* partial,
+                                   int* tickets, cudaStream_t stream) {
+  if (ntiles <= 0) return 0;
+  if (max_r > PSGD_MAX_RANK || ncorr > PSGD_MAX_HIST) {
+    psgd_set_error("psgd_gemm_ffma_launch: rank %d or history %d beyond the compiled maximum", max_r, ncorr);
+    return -1;
+  }
+  GemmArgs a;
+  fill_args(a, mats, tiles, in, out, ncorr, corr_fac, corr_c, partial, tickets);
+  if (transposed) {
+    if (vec4) { PSGD_DISPATCH_RT(launch_nt, 4) } else { PSGD_DISPATCH_RT(launch_nt, 1) }
+  } else {
+    if (vec4) { PSGD_DISPATCH_RT(launch_nn, 4) } else { PSGD_DISPATCH_RT(launch_nn, 1) }
+  }
+}

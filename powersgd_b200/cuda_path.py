@@ -1,0 +1,597 @@
+"""Drives the native sm_100a kernels for the compressor core and the flat all-reduce.
+
+Per optimizer step the reference issues several hundred small PyTorch ops
+(powersgd/powersgd.py:146-235). Here a step is, for T half-iterations:
+
+    T x [ orthonormalise (1 launch) -> grouped product (1-2 launches) -> all-reduce of the
+          fresh factor ]  ->  decompress + error feedback (+ SGD) (1-2 launches)
+
+over ALL shape groups at once. The gradient matrices are addressed in place through a
+pointer table (no `torch.stack`, no un-batching copies), the deflation between half-iterations
+is algebraic (small r x r corrections), and the residual is written exactly once.
+
+Factor bookkeeping for half-iteration t of a step (left = the P side is the input):
+
+    left :  Lloc = Lsum = orth(P)      Rloc = local M^T P      Rsum = sum over workers
+    right:  Rloc = Rsum = orth(Q)      Lloc = local M Q        Lsum = sum over workers
+
+    residual = M - sum_t Lloc_t Rloc_t^T        update = (1/W) sum_t Lsum_t Rsum_t^T
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .ops import layout, native
+from .utils import is_distributed, world_size
+
+
+def _stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _ptr_array(tensors: Sequence[torch.Tensor]):
+    arr = (ctypes.c_void_p * max(len(tensors), 1))()
+    for i, t in enumerate(tensors):
+        arr[i] = t.data_ptr()
+    return arr
+
+
+def _to_device(array: np.ndarray, device: torch.device) -> torch.Tensor:
+    raw = torch.from_numpy(np.ascontiguousarray(array).view(np.uint8).reshape(-1).copy())
+    return raw.to(device, non_blocking=False)
+
+
+def _split_even(total: int, max_chunk: int, multiple: int) -> List[Tuple[int, int]]:
+    """Cut [0, total) into near-equal chunks of at most `max_chunk`, starts on `multiple`."""
+    if total <= max_chunk:
+        return [(0, total)]
+    parts = -(-total // max_chunk)
+    size = -(-total // parts)
+    size = -(-size // multiple) * multiple
+    out, start = [], 0
+    while start < total:
+        out.append((start, min(size, total - start)))
+        start += size
+    return out
+
+
+class TilePlan:
+    """Static tile lists (independent of tensor addresses) for one CompressionPlan."""
+
+    def __init__(self, plan, lib):
+        self.plan = plan
+        mats = []  # (group index, position, compressed-list index)
+        for gi, g in enumerate(plan.groups):
+            for pos, idx in enumerate(g.members):
+                mats.append((gi, pos, idx))
+        self.mats = mats
+        self.max_r = max((g.r for g in plan.groups), default=1)
+        if self.max_r > layout.MAX_RANK:
+            raise ValueError(f"rank {self.max_r} exceeds the compiled maximum {layout.MAX_RANK}")
+        self.rt = lib.psgd_gemm_template_rank(self.max_r)
+        self.total_elems = sum(g.n * g.m * g.batch for g in plan.groups)
+        nt_rows_cap = lib.psgd_gemm_nt_max_rows(self.max_r)
+        self.nt_rows = min(nt_rows_cap, 128 if self.total_elems < (64 << 20) else 256)
+        self.nn_rows = lib.psgd_gemm_nn_tile_rows(self.max_r)
+        self.nn_cols_cap = 1024
+
+    def vec_ok(self, mi: int) -> bool:
+        g = self.plan.groups[self.mats[mi][0]]
+        return g.m % 4 == 0
+
+    def build(self, vec_flags: Sequence[bool]):
+        """Tile arrays split by vector width. Returns dict name -> {4: array, 1: array}."""
+        nt = {4: [], 1: []}
+        nn = {4: [], 1: []}
+        fin = {4: [], 1: []}
+        ticket = 0
+        nt_slots = nn_slots = 0
+        for mi, (gi, _pos, _idx) in enumerate(self.mats):
+            g = self.plan.groups[gi]
+            v = 4 if vec_flags[mi] else 1
+            row_blocks = _split_even(g.n, self.nt_rows, 1)
+            for c0 in range(0, g.m, 128):
+                cols = min(128, g.m - c0)
+                for si, (r0, rows) in enumerate(row_blocks):
+                    nt[v].append((mi, r0, rows, c0, cols, si, len(row_blocks), ticket, nt_slots, (0, 0, 0)))
+                ticket += 1
+                nt_slots += len(row_blocks)
+            col_blocks = _split_even(g.m, self.nn_cols_cap, 128)
+            for r0 in range(0, g.n, self.nn_rows):
+                rows = min(self.nn_rows, g.n - r0)
+                for si, (c0, cols) in enumerate(col_blocks):
+                    nn[v].append((mi, r0, rows, c0, cols, si, len(col_blocks), ticket, nn_slots, (0, 0, 0)))
+                ticket += 1
+                nn_slots += len(col_blocks)
+            for r0 in range(0, g.n, 32):
+                for c0 in range(0, g.m, 128):
+                    fin[v].append((mi, r0, min(32, g.n - r0), c0, min(128, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
+        self.n_tickets = max(ticket, 1)
+        self.partial_floats = max(nt_slots * 128 * self.rt, nn_slots * self.nn_rows * self.rt, 1)
+
+        def arr(items):
+            return np.array(items, dtype=layout.TILE_DTYPE) if items else np.zeros(0, dtype=layout.TILE_DTYPE)
+
+        return {
+            "nt": {k: arr(v) for k, v in nt.items()},
+            "nn": {k: arr(v) for k, v in nn.items()},
+            "fin": {k: arr(v) for k, v in fin.items()},
+        }
+
+    def orth_units(self, side: str) -> np.ndarray:
+        units = []
+        mi = 0
+        for g in self.plan.groups:
+            length = g.n if side == "p" else g.m
+            base = g.p_offset if side == "p" else g.q_offset
+            if g.r == 1:
+                units.append((base, length, g.batch, 1, mi, (0, 0, 0)))
+            else:
+                for b in range(g.batch):
+                    units.append((base + b * length * g.r, length, 1, g.r, mi + b, (0, 0, 0)))
+            mi += g.batch
+        return np.array(units, dtype=layout.ORTH_UNIT_DTYPE)
+
+
+class NativeCompressor:
+    """Runs `BasicPowerSGD.aggregate` on the GPU with the in-tree kernels."""
+
+    def __init__(self, core):
+        self.core = core
+        self.lib = native.lib()
+        self.device = core.device
+        self.plan = core.plan
+        self.tiles = TilePlan(core.plan, self.lib)
+        self.T = core.config.num_iters_per_step
+        if self.T > layout.MAX_HIST:
+            raise ValueError(f"num_iters_per_step {self.T} exceeds the compiled maximum {layout.MAX_HIST}")
+        nm = len(self.tiles.mats)
+        cap = max(self.plan.p_total, self.plan.q_total, 1)
+        f32 = dict(device=self.device, dtype=torch.float32)
+        self.h_in = [torch.zeros(cap, **f32) for _ in range(self.T)]
+        self.h_loc = [torch.zeros(cap, **f32) for _ in range(self.T)]
+        self.h_sum = [torch.zeros(cap, **f32) for _ in range(self.T)]
+        self.cmat = [[torch.zeros(nm * layout.CMAT_STRIDE, **f32) for _ in range(t)] for t in range(self.T)]
+        self.units = {s: _to_device(self.tiles.orth_units(s), self.device) for s in ("p", "q")}
+        self.n_units = {s: len(self.tiles.orth_units(s)) for s in ("p", "q")}
+        self._key = None
+        self._out_arena: Optional[torch.Tensor] = None
+        self._hyper_dev = _to_device(self._default_hyper(), self.device)
+        self.launches = 0  # kernels launched by the last aggregate()
+
+    @staticmethod
+    def _default_hyper() -> np.ndarray:
+        h = np.zeros(1, dtype=layout.HYPER_DTYPE)
+        h["grad_scale"] = 1.0
+        h["one_minus_dampening"] = 1.0
+        return h
+
+    # -- descriptors -----------------------------------------------------------------------
+    def _bind(
+        self,
+        grads: Sequence[torch.Tensor],
+        params: Optional[Sequence[torch.Tensor]] = None,
+        moms: Optional[Sequence[Optional[torch.Tensor]]] = None,
+        hyper_index: Optional[Sequence[int]] = None,
+        need_out: bool = True,
+    ) -> None:
+        key = (
+            tuple(g.data_ptr() for g in grads),
+            None if params is None else tuple(p.data_ptr() for p in params),
+            None if moms is None else tuple(0 if m is None else m.data_ptr() for m in moms),
+            need_out,
+        )
+        if key == self._key:
+            return
+        for g in grads:
+            if not g.is_contiguous() or g.dtype != torch.float32 or g.device != self.device:
+                raise ValueError("native PowerSGD needs contiguous float32 gradients on its device")
+        if need_out and self._out_arena is None:
+            self._out_arena = torch.empty(self.tiles.total_elems, device=self.device, dtype=torch.float32)
+        where = self.plan.locate()
+        descs = np.zeros(len(self.tiles.mats), dtype=layout.MAT_DTYPE)
+        vec = []
+        out_views: List[Optional[torch.Tensor]] = [None] * len(grads)
+        cursor = 0
+        # output arena is laid out in compressed-list order so that views are plain slices
+        out_offsets = []
+        for g in grads:
+            out_offsets.append(cursor)
+            cursor += g.numel()
+        for mi, (gi, pos, idx) in enumerate(self.tiles.mats):
+            g = self.plan.groups[gi]
+            d = descs[mi]
+            d["grad"] = grads[idx].data_ptr()
+            d["param"] = 0 if params is None else params[idx].data_ptr()
+            d["mom"] = 0 if (moms is None or moms[idx] is None) else moms[idx].data_ptr()
+            if need_out:
+                view = self._out_arena[out_offsets[idx] : out_offsets[idx] + grads[idx].numel()]
+                out_views[idx] = view.view(grads[idx].shape)
+                d["out"] = view.data_ptr()
+            d["n"], d["m"], d["r"] = g.n, g.m, g.r
+            d["p_off"] = g.p_offset + pos * g.n * g.r
+            d["q_off"] = g.q_offset + pos * g.m * g.r
+            d["grp_p_off"], d["grp_p_len"] = g.p_offset, g.p_numel
+            d["grp_q_off"], d["grp_q_len"] = g.q_offset, g.q_numel
+            d["hyper"] = 0 if hyper_index is None else hyper_index[idx]
+            d["index"] = mi
+            ptrs = [int(d["grad"]), int(d["param"]), int(d["mom"]), int(d["out"])]
+            vec.append(g.m % 4 == 0 and all(p % 16 == 0 for p in ptrs))
+        assert where is not None
+        self._mats_dev = _to_device(descs, self.device)
+        tile_arrays = self.tiles.build(vec)
+        self._tiles_dev: Dict[str, Dict[int, Tuple[torch.Tensor, int]]] = {}
+        for name, by_vec in tile_arrays.items():
+            self._tiles_dev[name] = {
+                v: (_to_device(a, self.device) if len(a) else None, len(a)) for v, a in by_vec.items()
+            }
+        self._partial = torch.empty(self.tiles.partial_floats, device=self.device, dtype=torch.float32)
+        self._tickets = torch.zeros(self.tiles.n_tickets, device=self.device, dtype=torch.int32)
+        self._out_views = out_views
+        self._key = key
+
+    # -- phases ----------------------------------------------------------------------------
+    def _orth(self, side: str, x: torch.Tensor, copy_to: torch.Tensor, prev: List[torch.Tensor], cm: List[torch.Tensor]):
+        code = self.lib.psgd_orth_launch(
+            _ptr(self.units[side]),
+            self.n_units[side],
+            self.tiles.max_r,
+            _ptr(x),
+            _ptr(copy_to),
+            len(prev),
+            ctypes.cast(_ptr_array(prev), ctypes.c_void_p),
+            ctypes.cast(_ptr_array(cm), ctypes.c_void_p),
+            _stream_ptr(),
+        )
+        native.check(code, "psgd_orth_launch")
+        self.launches += 1
+
+    def _gemm(self, transposed: bool, fin: torch.Tensor, fout: torch.Tensor, corr_fac, corr_c):
+        name = "nt" if transposed else "nn"
+        for v in (4, 1):
+            tiles, count = self._tiles_dev[name][v]
+            if count == 0:
+                continue
+            code = self.lib.psgd_gemm_ffma_launch(
+                1 if transposed else 0,
+                1 if v == 4 else 0,
+                self.tiles.max_r,
+                _ptr(self._mats_dev),
+                _ptr(tiles),
+                count,
+                _ptr(fin),
+                _ptr(fout),
+                len(corr_fac),
+                ctypes.cast(_ptr_array(corr_fac), ctypes.c_void_p),
+                ctypes.cast(_ptr_array(corr_c), ctypes.c_void_p),
+                _ptr(self._partial),
+                _ptr(self._tickets),
+                _stream_ptr(),
+            )
+            native.check(code, "psgd_gemm_ffma_launch")
+            self.launches += 1
+
+    def _finalize(self, sides: List[bool], fused_sgd: bool, workers: int):
+        lloc, rloc, lsum, rsum = [], [], [], []
+        for t, left in enumerate(sides):
+            if left:
+                lloc.append(self.h_in[t]); lsum.append(self.h_in[t])
+                rloc.append(self.h_loc[t]); rsum.append(self.h_sum[t])
+            else:
+                rloc.append(self.h_in[t]); rsum.append(self.h_in[t])
+                lloc.append(self.h_loc[t]); lsum.append(self.h_sum[t])
+        for v in (4, 1):
+            tiles, count = self._tiles_dev["fin"][v]
+            if count == 0:
+                continue
+            code = self.lib.psgd_finalize_launch(
+                1 if v == 4 else 0,
+                _ptr(self._mats_dev),
+                _ptr(tiles),
+                count,
+                _ptr(self._hyper_dev),
+                len(sides),
+                ctypes.cast(_ptr_array(lloc), ctypes.c_void_p),
+                ctypes.cast(_ptr_array(rloc), ctypes.c_void_p),
+                ctypes.cast(_ptr_array(lsum), ctypes.c_void_p),
+                ctypes.cast(_ptr_array(rsum), ctypes.c_void_p),
+                1.0 / workers,
+                1 if fused_sgd else 0,
+                _stream_ptr(),
+            )
+            native.check(code, "psgd_finalize_launch")
+            self.launches += 1
+
+    def _half_iterations(self) -> List[bool]:
+        core = self.core
+        workers = world_size()
+        sides: List[bool] = []
+        for t in range(self.T):
+            left = (core.step_counter * self.T + t) % 2 == 0
+            sides.append(left)
+            side = "p" if left else "q"
+            state_in = core._ps_buffer if left else core._qs_buffer
+            state_out = core._qs_buffer if left else core._ps_buffer
+            # earlier LOCAL factors on the input side (cross products) and on the output side (corrections)
+            same, other = [], []
+            for i in range(t):
+                in_side_i = self.h_in[i] if sides[i] == left else self.h_loc[i]
+                out_side_i = self.h_loc[i] if sides[i] == left else self.h_in[i]
+                same.append(in_side_i)
+                other.append(out_side_i)
+            self._orth(side, state_in, self.h_in[t], same, self.cmat[t])
+            self._gemm(left, self.h_in[t], self.h_loc[t], other, self.cmat[t])
+            total = state_out.numel()
+            if workers > 1:
+                self.h_sum[t][:total].copy_(self.h_loc[t][:total])
+                self._allreduce_sum(self.h_sum[t][:total])
+                state_out.copy_(self.h_sum[t][:total])
+            else:
+                state_out.copy_(self.h_loc[t][:total])
+        return sides
+
+    def _allreduce_sum(self, flat: torch.Tensor) -> None:
+        dist.all_reduce(flat)
+
+    # -- public ----------------------------------------------------------------------------
+    def aggregate(self, gradients: List[torch.Tensor]) -> List[torch.Tensor]:
+        self.launches = 0
+        self._bind(gradients)
+        workers = world_size()
+        if workers == 1:
+            saved = self.h_sum
+            self.h_sum = self.h_loc
+        try:
+            sides = self._half_iterations()
+            self._finalize(sides, fused_sgd=False, workers=workers)
+        finally:
+            if workers == 1:
+                self.h_sum = saved
+        return list(self._out_views)
+
+    def aggregate_and_step(
+        self,
+        gradients: List[torch.Tensor],
+        params: List[torch.Tensor],
+        moms: List[Optional[torch.Tensor]],
+        hyper_index: List[int],
+        hyper_dev: torch.Tensor,
+    ) -> None:
+        """Same as `aggregate`, but applies SGD to `params` inside the last kernel instead of
+        materialising the averaged gradients."""
+        self.launches = 0
+        self._bind(gradients, params, moms, hyper_index, need_out=False)
+        workers = world_size()
+        keep = self._hyper_dev
+        self._hyper_dev = hyper_dev
+        if workers == 1:
+            saved = self.h_sum
+            self.h_sum = self.h_loc
+        try:
+            sides = self._half_iterations()
+            self._finalize(sides, fused_sgd=True, workers=workers)
+        finally:
+            self._hyper_dev = keep
+            if workers == 1:
+                self.h_sum = saved
+
+
+class NativeFlatAllReduce:
+    """Mean of a list of float32 tensors through one flat buffer, with the packing, the 1/W
+    scale, the zeroing of the inputs and (optionally) the SGD update done by one multi-tensor
+    kernel on each side of the collective."""
+
+    def __init__(self):
+        self.lib = native.lib()
+        self._key = None
+        self.launches = 0
+
+    def _bind(self, grads, params=None, moms=None, hyper_index=None, need_out=True):
+        key = (
+            tuple(g.data_ptr() for g in grads),
+            None if params is None else tuple(p.data_ptr() for p in params),
+            None if moms is None else tuple(0 if m is None else m.data_ptr() for m in moms),
+            need_out,
+        )
+        if key == self._key:
+            return
+        device = grads[0].device
+        total = sum(g.numel() for g in grads)
+        self._flat = torch.empty(total, device=device, dtype=torch.float32)
+        self._out = torch.empty(total, device=device, dtype=torch.float32) if need_out else None
+        items = np.zeros(len(grads), dtype=layout.FLAT_DTYPE)
+        per_block = self.lib.psgd_flat_block_elems()
+        block_item, block_first = [], []
+        views, cursor = [], 0
+        for i, g in enumerate(grads):
+            if not g.is_contiguous() or g.dtype != torch.float32:
+                raise ValueError("native flat all-reduce needs contiguous float32 tensors")
+            it = items[i]
+            it["grad"] = g.data_ptr()
+            it["param"] = 0 if params is None else params[i].data_ptr()
+            it["mom"] = 0 if (moms is None or moms[i] is None) else moms[i].data_ptr()
+            if need_out:
+                v = self._out[cursor : cursor + g.numel()]
+                views.append(v.view(g.shape))
+                it["out"] = v.data_ptr()
+            it["numel"] = g.numel()
+            it["flat_off"] = cursor
+            it["hyper"] = 0 if hyper_index is None else hyper_index[i]
+            for first in range(0, g.numel(), per_block):
+                block_item.append(i)
+                block_first.append(first)
+            cursor += g.numel()
+        self._items_dev = _to_device(items, device)
+        self._block_item = torch.tensor(block_item, dtype=torch.int32, device=device)
+        self._block_first = torch.tensor(block_first, dtype=torch.int32, device=device)
+        self._nblocks = len(block_item)
+        self._views = views
+        self._hyper_dev = _to_device(NativeCompressor._default_hyper(), device)
+        self._key = key
+
+    def _launch(self, mode: int, hyper_dev: torch.Tensor, divisor: float) -> None:
+        code = self.lib.psgd_flat_launch(
+            mode,
+            _ptr(self._items_dev),
+            _ptr(self._block_item),
+            _ptr(self._block_first),
+            self._nblocks,
+            _ptr(hyper_dev),
+            _ptr(self._flat),
+            float(divisor),
+            _stream_ptr(),
+        )
+        native.check(code, "psgd_flat_launch")
+        self.launches += 1
+
+    def aggregate(self, gradients: List[torch.Tensor]) -> List[torch.Tensor]:
+        self.launches = 0
+        self._bind(gradients)
+        workers = world_size()
+        if workers == 1:
+            self._launch(3, self._hyper_dev, 1.0)
+        else:
+            self._launch(0, self._hyper_dev, float(workers))
+            dist.all_reduce(self._flat)
+            self._launch(1, self._hyper_dev, 1.0)
+        return list(self._views)
+
+    def aggregate_and_step(self, gradients, params, moms, hyper_index, hyper_dev) -> None:
+        self.launches = 0
+        self._bind(gradients, params, moms, hyper_index, need_out=False)
+        workers = world_size()
+        if workers == 1:
+            self._launch(4, hyper_dev, 1.0)
+        else:
+            self._launch(0, hyper_dev, float(workers))
+            dist.all_reduce(self._flat)
+            self._launch(2, hyper_dev, 1.0)
+
+
+class FusedSGDDriver:
+    """Glue between `torch.optim.SGD` and the fused kernels.
+
+    Keeps `optimizer.state[p]["momentum_buffer"]` as the live momentum tensors (so optimizer
+    checkpoints stay valid), refreshes a small device table of per-group hyper-parameters
+    every step (learning-rate schedules keep working), and follows torch's first-step rule
+    that a fresh momentum buffer is the gradient itself.
+
+    The table travels through a ring of pinned host slots, one eager async copy per step, so
+    that a step recorded in a CUDA graph reads its hyper-parameters from device memory and
+    the host never overwrites a slot that a copy in flight still reads.
+    """
+
+    RING = 4
+
+    def __init__(self, agg):
+        self.agg = agg
+        self.device = agg.device
+        self._slots: List[torch.Tensor] = []
+        self._slot_events: List[Optional[torch.cuda.Event]] = []
+        self._cursor = 0
+        self._hyper_dev: Optional[torch.Tensor] = None
+        self._cache_key = None
+        self._flat_all = NativeFlatAllReduce()
+        self._flat_plain = NativeFlatAllReduce()
+        self.launches = 0
+
+    def _collect(self, optimizer):
+        groups = optimizer.param_groups
+        key = (id(optimizer), tuple(len(g["params"]) for g in groups), tuple(float(g["momentum"]) != 0.0 for g in groups))
+        fresh_groups = set()
+        if key != self._cache_key or any(
+            float(g["momentum"]) != 0.0 and optimizer.state[p].get("momentum_buffer") is None
+            for g in groups
+            for p in g["params"][:1]
+        ):
+            params, moms, index = [], [], []
+            for gi, group in enumerate(groups):
+                mu = float(group["momentum"])
+                for p in group["params"]:
+                    params.append(p)
+                    index.append(gi)
+                    if mu != 0.0:
+                        st = optimizer.state[p]
+                        if st.get("momentum_buffer") is None:
+                            st["momentum_buffer"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+                            fresh_groups.add(gi)
+                        moms.append(st["momentum_buffer"])
+                    else:
+                        moms.append(None)
+            self._params, self._moms, self._index = params, moms, index
+            self._grads = [p.grad.data for p in params]
+            self._cache_key = key
+        return fresh_groups
+
+    def prepare(self, optimizer) -> None:
+        """Host side of a step: momentum buffers, hyper-parameter table, async upload."""
+        fresh = self._collect(optimizer)
+        groups = optimizer.param_groups
+        table = np.zeros(len(groups), dtype=layout.HYPER_DTYPE)
+        for gi, group in enumerate(groups):
+            mu = float(group["momentum"])
+            row = table[gi]
+            row["lr"] = group["lr"]
+            row["momentum"] = mu
+            row["one_minus_dampening"] = 1.0 if gi in fresh else 1.0 - float(group["dampening"])
+            row["weight_decay"] = group["weight_decay"]
+            row["nesterov"] = 1 if group["nesterov"] else 0
+            row["has_momentum"] = 1 if mu != 0.0 else 0
+            row["grad_scale"] = 1.0
+        nbytes = table.nbytes
+        if self._hyper_dev is None or self._hyper_dev.numel() != nbytes:
+            self._slots = [torch.empty(nbytes, dtype=torch.uint8).pin_memory() for _ in range(self.RING)]
+            self._slot_events = [None] * self.RING
+            self._hyper_dev = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        i = self._cursor
+        self._cursor = (i + 1) % self.RING
+        if self._slot_events[i] is not None:
+            self._slot_events[i].synchronize()
+        self._slots[i].numpy()[:] = table.view(np.uint8).reshape(-1)
+        self._hyper_dev.copy_(self._slots[i], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._slot_events[i] = ev
+        # the residual tensors may have been replaced (e.g. after loading a checkpoint)
+        if any(p.grad.data_ptr() != g.data_ptr() for p, g in zip(self._params[:4], self._grads[:4])):
+            self._grads = [p.grad.data for p in self._params]
+
+    def step(self, optimizer, prepared: bool = False) -> None:
+        if not prepared:
+            self.prepare(optimizer)
+        agg = self.agg
+        hyper_dev, index, params, moms, grads = self._hyper_dev, self._index, self._params, self._moms, self._grads
+        if len(grads) != len(agg.is_compressed_mask):
+            raise ValueError("optimizer parameters do not match the aggregator's parameter list")
+        agg.step_counter += 1
+        if agg.step_counter <= agg.config.start_compressing_after_num_steps:
+            self._flat_all.aggregate_and_step(grads, params, moms, index, hyper_dev)
+            self.launches = self._flat_all.launches
+            return
+        mask = agg.is_compressed_mask
+        pick = lambda xs, keep: [x for x, k in zip(xs, mask) if k == keep]  # noqa: E731
+        core = agg._powersgd
+        self.launches = 0
+        if core.params:
+            if core._native is None:
+                core._native = NativeCompressor(core)
+            core._native.aggregate_and_step(
+                pick(grads, True), pick(params, True), pick(moms, True), pick(index, True), hyper_dev
+            )
+            core.step_counter += 1
+            self.launches += core._native.launches
+        plain = pick(grads, False)
+        if plain:
+            self._flat_plain.aggregate_and_step(
+                plain, pick(params, False), pick(moms, False), pick(index, False), hyper_dev
+            )
+            self.launches += self._flat_plain.launches

@@ -1,0 +1,145 @@
+"""Training-step engine: forward, backward, gradient aggregation and optimizer update as one
+replayable CUDA graph.
+
+The reference leaves the step to the user's Python loop (README.md:23-43): a few hundred
+eager launches for a CIFAR ResNet plus several hundred more inside `aggregate()`. On a B200
+that loop is bound by launch latency, not by the GPU. `TrainStep` keeps the same semantics
+(`loss.backward()` accumulates onto the residual left in `.grad`; no `zero_grad`) but records
+the whole step once and replays it:
+
+    step = TrainStep(model, loss_fn, optimizer, aggregator)
+    for x, y in loader:
+        loss = step(x, y)          # tensor on the device; call .item() when you need it
+
+Everything that changes between steps lives in device memory that the graph reads at replay
+time: the input batch (copied into static buffers), the learning-rate table (refreshed from
+pinned memory), the warm-start factors and the residuals. Steps that are structurally
+different run eagerly or get their own graph: the un-compressed warm-up phase, the first
+steps (cuDNN autotuning, lazy momentum buffers), and — for an odd `num_iters_per_step` — the
+two parities of the power iteration.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, Optional
+
+import torch
+
+from .optim import optimizer_step
+
+
+class TrainStep:
+    def __init__(
+        self,
+        model: torch.nn.Module,
+        loss_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
+        optimizer: torch.optim.Optimizer,
+        aggregator,
+        cuda_graph: bool = True,
+        eager_steps: int = 3,
+    ):
+        self.model = model
+        self.loss_fn = loss_fn
+        self.optimizer = optimizer
+        self.aggregator = aggregator
+        self.device = next(model.parameters()).device
+        self.use_graph = bool(cuda_graph) and self.device.type == "cuda"
+        self.eager_steps = max(int(eager_steps), 2)
+        self._steps_done = 0
+        self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self._static_x: Optional[torch.Tensor] = None
+        self._static_y: Optional[torch.Tensor] = None
+        self._static_loss: Optional[torch.Tensor] = None
+        self._pool = None
+        self._agg_events = None
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------------------------
+    def _eager(self, x: torch.Tensor, y: torch.Tensor, time_aggregate: bool = False) -> torch.Tensor:
+        loss = self.loss_fn(self.model(x), y)
+        loss.backward()
+        if time_aggregate and self.device.type == "cuda":
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            optimizer_step(self.optimizer, self.aggregator)
+            b.record()
+            self._agg_events = (a, b)
+        else:
+            optimizer_step(self.optimizer, self.aggregator)
+        fused = getattr(self.aggregator, "_fused", None)
+        if fused is not None:
+            self.launches_per_step = getattr(fused, "launches", 0)
+        return loss.detach()
+
+    @property
+    def aggregate_ms(self) -> Optional[float]:
+        """Device time of the aggregation + optimizer part of the last eagerly run step."""
+        if self._agg_events is None:
+            return None
+        a, b = self._agg_events
+        b.synchronize()
+        return a.elapsed_time(b)
+
+    def _parity(self) -> int:
+        core = getattr(self.aggregator, "_powersgd", None)
+        if core is None:
+            return 0
+        return (core.step_counter * core.config.num_iters_per_step) % 2
+
+    def _graphable_now(self) -> bool:
+        if not self.use_graph or self._steps_done < self.eager_steps:
+            return False
+        if self._graphs:
+            return True
+        compressing = getattr(self.aggregator, "compressing", True)
+        fused_ok = getattr(self.aggregator, "supports_fused_step", lambda _o: False)(self.optimizer)
+        return bool(compressing) and bool(fused_ok)
+
+    def _bump_counters(self) -> None:
+        agg = self.aggregator
+        agg.step_counter += 1
+        core = getattr(agg, "_powersgd", None)
+        if core is not None and core.params:
+            core.step_counter += 1
+
+    def _capture(self, parity: int) -> None:
+        agg = self.aggregator
+        saved = (agg.step_counter, agg._powersgd.step_counter)
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, pool=self._pool):
+            loss = self.loss_fn(self.model(self._static_x), self._static_y)
+            loss.backward()
+            agg.fused_step(self.optimizer, prepared=True)
+            if self._static_loss is None:
+                self._static_loss = loss.detach()
+            else:
+                self._static_loss.copy_(loss.detach())
+        if self._pool is None:
+            self._pool = graph.pool()
+        # capturing ran the host side of the step (counters) but not the kernels: rewind
+        agg.step_counter, agg._powersgd.step_counter = saved
+        self._graphs[parity] = graph
+
+    def __call__(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        if not self._graphable_now():
+            loss = self._eager(x, y, time_aggregate=True)
+            self._steps_done += 1
+            return loss
+        if self._static_x is None:
+            self._static_x = torch.empty_like(x, device=self.device)
+            self._static_y = torch.empty_like(y, device=self.device)
+        if x.shape != self._static_x.shape or y.shape != self._static_y.shape:
+            loss = self._eager(x, y)  # ragged last batch etc.
+            self._steps_done += 1
+            return loss
+        self._static_x.copy_(x, non_blocking=True)
+        self._static_y.copy_(y, non_blocking=True)
+        parity = self._parity()
+        if parity not in self._graphs:
+            self._capture(parity)
+        # host-side refresh of what the graph reads from memory (learning rates etc.)
+        self.aggregator._fused.prepare(self.optimizer)
+        self._graphs[parity].replay()
+        self._bump_counters()
+        self._steps_done += 1
+        return self._static_loss

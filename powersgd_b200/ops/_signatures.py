@@ -1,0 +1,43 @@
+"""ctypes prototypes of the exported C entry points."""
+import ctypes as C
+
+vp = C.c_void_p
+i32 = C.c_int
+f32 = C.c_float
+
+
+def declare(lib) -> None:
+    lib.psgd_last_error.restype = C.c_char_p
+    lib.psgd_last_error.argtypes = []
+    lib.psgd_version.restype = i32
+    lib.psgd_device_info.restype = i32
+    lib.psgd_device_info.argtypes = [C.POINTER(i32)] * 4
+
+    lib.psgd_orth_launch.restype = i32
+    lib.psgd_orth_launch.argtypes = [vp, i32, i32, vp, vp, i32, vp, vp, vp]
+
+    lib.psgd_gemm_nn_tile_rows.restype = i32
+    lib.psgd_gemm_nn_tile_rows.argtypes = [i32]
+    lib.psgd_gemm_nt_max_rows.restype = i32
+    lib.psgd_gemm_nt_max_rows.argtypes = [i32]
+    lib.psgd_gemm_template_rank.restype = i32
+    lib.psgd_gemm_template_rank.argtypes = [i32]
+    lib.psgd_gemm_ffma_launch.restype = i32
+    lib.psgd_gemm_ffma_launch.argtypes = [i32, i32, i32, vp, vp, i32, vp, vp, i32, vp, vp, vp, vp, vp]
+
+    lib.psgd_finalize_launch.restype = i32
+    lib.psgd_finalize_launch.argtypes = [i32, vp, vp, i32, vp, i32, vp, vp, vp, vp, f32, i32, vp]
+
+    lib.psgd_flat_block_elems.restype = i32
+    lib.psgd_flat_block_elems.argtypes = []
+    lib.psgd_flat_launch.restype = i32
+    lib.psgd_flat_launch.argtypes = [i32, vp, vp, vp, i32, vp, vp, f32, vp]
+
+    for name, sig in _OPTIONAL.items():
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.restype, fn.argtypes = sig
+
+
+# entry points that later translation units add; declared when present
+_OPTIONAL = {}

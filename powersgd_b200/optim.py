@@ -13,7 +13,14 @@ def optimizer_step(optimizer: torch.optim.Optimizer, aggregator: Aggregator) -> 
 
     The next `backward()` accumulates onto that residual, which is how error feedback is
     realised — so the caller must NOT call `optimizer.zero_grad()` between steps.
+
+    With the native back end and a plain `torch.optim.SGD`, aggregation, error feedback and
+    the parameter update run as one fused sequence of kernels (`PowerSGD.fused_step`).
     """
+    fused = getattr(aggregator, "supports_fused_step", None)
+    if fused is not None and fused(optimizer):
+        aggregator.fused_step(optimizer)
+        return
     params = params_in_optimizer(optimizer)
     residuals = [p.grad.data for p in params]
     averaged = aggregator.aggregate(residuals)  # `residuals` now hold what was not sent
