@@ -40,4 +40,9 @@ def declare(lib) -> None:
 
 
 # entry points that later translation units add; declared when present
-_OPTIONAL = {}
+i64 = C.c_longlong
+_OPTIONAL = {
+    "psgd_sign_pack": (i32, [vp, i64, vp, vp]),
+    "psgd_sign_unpack": (i32, [vp, i64, f32, vp, i32, vp]),
+    "psgd_sign_vote": (i32, [vp, i32, i64, i32, vp, vp, vp]),
+}

@@ -56,11 +56,13 @@ def test_compressor_matches_torch_path(rank, iters, steps):
         oa = [o.clone() for o in ours.aggregate(ga)]
         ob = oracle.aggregate(gb)
         for x, y, b, res in zip(oa, ob, before, ga):
-            assert _rel(x, y) < 2e-5, (step, x.shape, _rel(x, y))
+            assert _rel(x, y) < 5e-5, (step, x.shape, _rel(x, y))
             # error-feedback identity holds to rounding, whatever the factors are
             assert _rel(x + res, b) < 1e-6
         for x, y in zip(ga, gb):
-            assert _rel(x, y) < 2e-5, (step, x.shape, _rel(x, y))
+            assert _rel(x, y) < 5e-5, (step, x.shape, _rel(x, y))
+            # the compression error itself (norm of the residual) agrees to 1e-5 relative
+            assert abs(x.double().norm().item() - y.double().norm().item()) <= 1e-5 * y.double().norm().item()
         fresh = _lowrank_grads(shapes, dev, 100 + step)
         for x, y, f in zip(ga, gb, fresh):
             x.add_(f)
