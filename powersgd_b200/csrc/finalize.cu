@@ -12,7 +12,7 @@
 //     or        SGD with momentum / dampening / nesterov / weight decay applied to `param`
 // HBM traffic: read + write M, plus param / momentum when fused. The rank-(T*r) updates run on
 // FP32 FMAs from shared-memory panels (4x4 register micro-tiles).
-#include "psgd_common.cuh"
+#include "psgd_comm.cuh"
 
 constexpr int FIN_THREADS = 256;
 constexpr int FIN_ROWS = 32;    // 8 warps x 4 rows
@@ -213,6 +213,9 @@ struct FlatArgs {
   int mode;  // 0: pack (flat = grad / divisor, grad = 0)
              // 1: unpack (out = flat) ; 2: unpack + SGD on param
              // 3: local (no communication): out = grad / divisor, grad = 0 ; 4: local + SGD
+             // 5: pack + push to every peer's slot, then publish the epoch (in-kernel all-reduce, part 1)
+             // 6: wait for all peers, sum the slots in rank order -> out ; 7: same + SGD (part 2)
+  const PsgdCommDev* comm;
 };
 
 constexpr int FLAT_THREADS = 256;
@@ -222,6 +225,13 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
   const PsgdFlat it = a.items[a.block_item[blockIdx.x]];
   const long long first = a.block_first[blockIdx.x];
   const PsgdHyper h = a.hyper[it.hyper];
+  PsgdCommDev c;
+  int e1 = 0;
+  if (a.mode >= 5) {
+    c = *a.comm;
+    e1 = *c.epoch + 1;
+    if (a.mode >= 6) psgd_comm_wait_all(c, e1);
+  }
   for (int e = threadIdx.x; e < FLAT_PER_BLOCK; e += FLAT_THREADS) {
     const long long i = first + e;
     if (i >= it.numel) break;
@@ -230,13 +240,21 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
       a.flat[it.flat_off + i] = it.grad[i] / a.divisor;
       it.grad[i] = 0.f;
       continue;
+    } else if (a.mode == 5) {
+      const float v = it.grad[i] / a.divisor;
+      it.grad[i] = 0.f;
+      for (int p = 0; p < c.world; ++p) psgd_comm_slot(c, p, e1, c.rank)[it.flat_off + i] = v;
+      continue;
     } else if (a.mode == 1 || a.mode == 2) {
       g = a.flat[it.flat_off + i];
+    } else if (a.mode >= 6) {
+      g = 0.f;
+      for (int r = 0; r < c.world; ++r) g += __ldcg(psgd_comm_slot(c, c.rank, e1, r) + it.flat_off + i);
     } else {
       g = it.grad[i] / a.divisor;
       it.grad[i] = 0.f;
     }
-    if (a.mode == 2 || a.mode == 4) {
+    if (a.mode == 2 || a.mode == 4 || a.mode == 7) {
       float p = it.param[i];
       float mo = h.has_momentum ? it.mom[i] : 0.f;
       psgd_sgd_update(g, p, &mo, h);
@@ -246,13 +264,31 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
       it.out[i] = g;
     }
   }
+  if (a.mode >= 5) {
+    // count this CTA in; the last producer publishes, the last consumer closes the epoch
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int* counter = c.arrive + (a.mode == 5 ? 0 : 1);
+      if (psgd_atom_add_acqrel_gpu(counter, 1) == (int)gridDim.x - 1) {
+        *counter = 0;
+        if (a.mode == 5) psgd_comm_publish(c, e1);
+        else *c.epoch = e1;
+      }
+    }
+  }
 }
 
 PSGD_API int psgd_flat_block_elems() { return FLAT_PER_BLOCK; }
 
 PSGD_API int psgd_flat_launch(int mode, const void* items, const int* block_item, const int* block_first,
-                              int nblocks, const void* hyper, float* flat, float divisor, cudaStream_t stream) {
+                              int nblocks, const void* hyper, float* flat, float divisor, const void* comm,
+                              cudaStream_t stream) {
   if (nblocks <= 0) return 0;
+  if (mode >= 5 && comm == nullptr) {
+    psgd_set_error("psgd_flat_launch: mode %d needs a communication channel", mode);
+    return -1;
+  }
   FlatArgs a;
   a.items = (const PsgdFlat*)items;
   a.block_item = block_item;
@@ -261,6 +297,7 @@ PSGD_API int psgd_flat_launch(int mode, const void* items, const int* block_item
   a.flat = flat;
   a.divisor = divisor;
   a.mode = mode;
+  a.comm = (const PsgdCommDev*)comm;
   psgd_flat_kernel<<<nblocks, FLAT_THREADS, 0, stream>>>(a);
   PSGD_CUDA_OK(cudaGetLastError());
   return 0;

@@ -16,7 +16,7 @@
 // Tiles that cover the same output rows (NT: row blocks of one column block; NN: column
 // blocks of one row block) write partial sums to a scratch arena; the tile that arrives last
 // (arrival counter) adds them in a fixed order, so the result does not depend on scheduling.
-#include "psgd_common.cuh"
+#include "psgd_comm.cuh"
 
 constexpr int GEMM_THREADS = 256;
 constexpr int GEMM_WARPS = GEMM_THREADS / 32;
@@ -34,7 +34,26 @@ struct GemmArgs {
   const float* corr_c[PSGD_MAX_HIST];    // [mat][r*r] cross products
   float* partial;     // scratch for split tiles
   int* tickets;       // arrival counters (all zero between launches)
+  // Multi-GPU: the epilogue also pushes every finished factor row into slot[rank] of every
+  // peer's arena, and the CTA that arrives last (over `expected_ctas`, which may span several
+  // launches of one phase) publishes the next epoch. Null for a single worker.
+  const PsgdCommDev* comm;
+  int expected_ctas;
 };
+
+// Common tail of both product kernels: count this CTA in; the last one publishes.
+__device__ __forceinline__ void gemm_comm_tail(const GemmArgs& a) {
+  if (a.comm == nullptr) return;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const PsgdCommDev c = *a.comm;
+    if (psgd_atom_add_acqrel_gpu(c.arrive + 0, 1) == a.expected_ctas - 1) {
+      c.arrive[0] = 0;
+      psgd_comm_publish(c, *c.epoch + 1);
+    }
+  }
+}
 
 template <int RT>
 __host__ __device__ constexpr int nt_max_rows() { return RT <= 16 ? NT_MAX_ROWS : NT_MAX_ROWS / 2; }
@@ -125,6 +144,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) 
   }
 
   const int tile_elems = NT_TILE_COLS * RT;
+  bool owner = true;  // does this CTA write the output rows?
   if (t.nsplit > 1) {
     float* mine = a.partial + (long long)(t.slot0 + t.split) * tile_elems;
     for (int e = tid; e < tile_elems; e += GEMM_THREADS) __stcg(mine + e, sSum[e]);
@@ -132,20 +152,30 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) 
     __syncthreads();
     if (tid == 0) sLast = (psgd_atom_add_acqrel_gpu(a.tickets + t.ticket, 1) == t.nsplit - 1);
     __syncthreads();
-    if (!sLast) return;
-    __threadfence();
-    for (int e = tid; e < tile_elems; e += GEMM_THREADS) {
-      float s = 0.f;
-      for (int p = 0; p < t.nsplit; ++p) s += __ldcg(a.partial + (long long)(t.slot0 + p) * tile_elems + e);
-      sSum[e] = s;
+    owner = sLast != 0;
+    if (owner) {
+      __threadfence();
+      for (int e = tid; e < tile_elems; e += GEMM_THREADS) {
+        float s = 0.f;
+        for (int p = 0; p < t.nsplit; ++p) s += __ldcg(a.partial + (long long)(t.slot0 + p) * tile_elems + e);
+        sSum[e] = s;
+      }
+      if (tid == 0) a.tickets[t.ticket] = 0;  // ready for the next launch
+      __syncthreads();
     }
-    if (tid == 0) a.tickets[t.ticket] = 0;  // ready for the next launch
-    __syncthreads();
   }
 
-  // epilogue: subtract the deflation terms and store Q rows
+  // epilogue: subtract the deflation terms, store Q rows locally and push them to the peers
   float* __restrict__ qout = a.out + mt.q_off;
-  for (int e = tid; e < t.cols * r; e += GEMM_THREADS) {
+  float* push[PSGD_MAX_WORLD];
+  int npush = 0;
+  if (a.comm != nullptr && owner) {
+    const PsgdCommDev c = *a.comm;
+    const int e1 = *c.epoch + 1;
+    npush = c.world;
+    for (int p = 0; p < PSGD_MAX_WORLD; ++p) push[p] = p < c.world ? psgd_comm_slot(c, p, e1, c.rank) + mt.q_off : nullptr;
+  }
+  for (int e = tid; owner && e < t.cols * r; e += GEMM_THREADS) {
     const int lc = e / r, k = e % r;
     const int col = t.col0 + lc;
     float s = sSum[lc * RT + k];
@@ -157,7 +187,9 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) 
       s -= d;
     }
     qout[(long long)col * r + k] = s;
+    for (int p = 0; p < npush; ++p) push[p][(long long)col * r + k] = s;
   }
+  gemm_comm_tail(a);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -237,6 +269,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nn_kernel(GemmArgs a) 
   __syncthreads();
 
   constexpr int tile_elems = TILE_ROWS * RT;
+  bool owner = true;
   if (t.nsplit > 1) {
     float* mine = a.partial + (long long)(t.slot0 + t.split) * tile_elems;
     for (int e = tid; e < tile_elems; e += GEMM_THREADS) __stcg(mine + e, sSum[e]);
@@ -244,19 +277,29 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nn_kernel(GemmArgs a) 
     __syncthreads();
     if (tid == 0) sLast = (psgd_atom_add_acqrel_gpu(a.tickets + t.ticket, 1) == t.nsplit - 1);
     __syncthreads();
-    if (!sLast) return;
-    __threadfence();
-    for (int e = tid; e < tile_elems; e += GEMM_THREADS) {
-      float s = 0.f;
-      for (int p = 0; p < t.nsplit; ++p) s += __ldcg(a.partial + (long long)(t.slot0 + p) * tile_elems + e);
-      sSum[e] = s;
+    owner = sLast != 0;
+    if (owner) {
+      __threadfence();
+      for (int e = tid; e < tile_elems; e += GEMM_THREADS) {
+        float s = 0.f;
+        for (int p = 0; p < t.nsplit; ++p) s += __ldcg(a.partial + (long long)(t.slot0 + p) * tile_elems + e);
+        sSum[e] = s;
+      }
+      if (tid == 0) a.tickets[t.ticket] = 0;
+      __syncthreads();
     }
-    if (tid == 0) a.tickets[t.ticket] = 0;
-    __syncthreads();
   }
 
   float* __restrict__ pout = a.out + mt.p_off;
-  for (int e = tid; e < t.rows * r; e += GEMM_THREADS) {
+  float* push[PSGD_MAX_WORLD];
+  int npush = 0;
+  if (a.comm != nullptr && owner) {
+    const PsgdCommDev c = *a.comm;
+    const int e1 = *c.epoch + 1;
+    npush = c.world;
+    for (int p = 0; p < PSGD_MAX_WORLD; ++p) push[p] = p < c.world ? psgd_comm_slot(c, p, e1, c.rank) + mt.p_off : nullptr;
+  }
+  for (int e = tid; owner && e < t.rows * r; e += GEMM_THREADS) {
     const int lr = e / r, k = e % r;
     const int row = t.row0 + lr;
     float s = sSum[lr * RT + k];
@@ -268,14 +311,17 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nn_kernel(GemmArgs a) 
       s -= d;
     }
     pout[(long long)row * r + k] = s;
+    for (int p = 0; p < npush; ++p) push[p][(long long)row * r + k] = s;
   }
+  gemm_comm_tail(a);
 }
 
 // ------------------------------------------------------------------------------------------
 // Host launchers
 // ------------------------------------------------------------------------------------------
 static void fill_args(GemmArgs& a, const void* mats, const void* tiles, const float* in, float* out, int ncorr,
-                      const float* const* corr_fac, const float* const* corr_c, float* partial, int* tickets) {
+                      const float* const* corr_fac, const float* const* corr_c, float* partial, int* tickets,
+                      const void* comm, int expected_ctas) {
   a.mats = (const PsgdMat*)mats;
   a.tiles = (const PsgdTile*)tiles;
   a.in = in;
@@ -287,6 +333,8 @@ static void fill_args(GemmArgs& a, const void* mats, const void* tiles, const fl
   }
   a.partial = partial;
   a.tickets = tickets;
+  a.comm = (const PsgdCommDev*)comm;
+  a.expected_ctas = expected_ctas;
 }
 
 template <int RT, int VEC>
@@ -334,14 +382,14 @@ PSGD_API int psgd_gemm_template_rank(int max_r) {
 PSGD_API int psgd_gemm_ffma_launch(int transposed, int vec4, int max_r, const void* mats, const void* tiles,
                                    int ntiles, const float* in, float* out, int ncorr,
                                    const float* const* corr_fac, const float* const* corr_c, float* partial,
-                                   int* tickets, cudaStream_t stream) {
+                                   int* tickets, const void* comm, int expected_ctas, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
   if (max_r > PSGD_MAX_RANK || ncorr > PSGD_MAX_HIST) {
     psgd_set_error("psgd_gemm_ffma_launch: rank %d or history %d beyond the compiled maximum", max_r, ncorr);
     return -1;
   }
   GemmArgs a;
-  fill_args(a, mats, tiles, in, out, ncorr, corr_fac, corr_c, partial, tickets);
+  fill_args(a, mats, tiles, in, out, ncorr, corr_fac, corr_c, partial, tickets, comm, expected_ctas);
   if (transposed) {
     if (vec4) { PSGD_DISPATCH_RT(launch_nt, 4) } else { PSGD_DISPATCH_RT(launch_nt, 1) }
   } else {

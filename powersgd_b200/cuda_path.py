@@ -20,6 +20,7 @@ Factor bookkeeping for half-iteration t of a step (left = the P side is the inpu
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -167,6 +168,13 @@ class NativeCompressor:
         self._out_arena: Optional[torch.Tensor] = None
         self._hyper_dev = _to_device(self._default_hyper(), self.device)
         self.launches = 0  # kernels launched by the last aggregate()
+        # multi-GPU: factors are all-reduced by the product kernels themselves (peer pushes) plus
+        # a small consumer kernel; PSGD_B200_COMM=nccl selects the library all-reduce instead
+        self.comm = None
+        if world_size() > 1 and os.environ.get("PSGD_B200_COMM", "p2p") == "p2p":
+            from .parallel.symm import Channel
+
+            self.comm = Channel(cap)
 
     @staticmethod
     def _default_hyper() -> np.ndarray:
@@ -257,6 +265,7 @@ class NativeCompressor:
 
     def _gemm(self, transposed: bool, fin: torch.Tensor, fout: torch.Tensor, corr_fac, corr_c):
         name = "nt" if transposed else "nn"
+        expected = sum(self._tiles_dev[name][v][1] for v in (4, 1))
         for v in (4, 1):
             tiles, count = self._tiles_dev[name][v]
             if count == 0:
@@ -275,6 +284,8 @@ class NativeCompressor:
                 ctypes.cast(_ptr_array(corr_c), ctypes.c_void_p),
                 _ptr(self._partial),
                 _ptr(self._tickets),
+                self.comm.ptr if self.comm is not None else ctypes.c_void_p(0),
+                expected,
                 _stream_ptr(),
             )
             native.check(code, "psgd_gemm_ffma_launch")
@@ -331,7 +342,13 @@ class NativeCompressor:
             self._orth(side, state_in, self.h_in[t], same, self.cmat[t])
             self._gemm(left, self.h_in[t], self.h_loc[t], other, self.cmat[t])
             total = state_out.numel()
-            if workers > 1:
+            if workers > 1 and self.comm is not None:
+                code = self.lib.psgd_factor_reduce_launch(
+                    self.comm.ptr, ctypes.c_longlong(total), _ptr(self.h_sum[t]), _ptr(state_out), _stream_ptr()
+                )
+                native.check(code, "psgd_factor_reduce_launch")
+                self.launches += 1
+            elif workers > 1:
                 self.h_sum[t][:total].copy_(self.h_loc[t][:total])
                 self._allreduce_sum(self.h_sum[t][:total])
                 state_out.copy_(self.h_sum[t][:total])
@@ -390,10 +407,14 @@ class NativeFlatAllReduce:
     scale, the zeroing of the inputs and (optionally) the SGD update done by one multi-tensor
     kernel on each side of the collective."""
 
+    # one-shot pushes send (W-1) copies of the buffer; above this arena size use the library ring
+    P2P_ARENA_LIMIT_BYTES = 1 << 30
+
     def __init__(self):
         self.lib = native.lib()
         self._key = None
         self.launches = 0
+        self.comm = None
 
     def _bind(self, grads, params=None, moms=None, hyper_index=None, need_out=True):
         key = (
@@ -437,6 +458,19 @@ class NativeFlatAllReduce:
         self._views = views
         self._hyper_dev = _to_device(NativeCompressor._default_hyper(), device)
         self._key = key
+        workers = world_size()
+        if self.comm is not None and self.comm.cap < total:
+            self.comm.close()
+            self.comm = None
+        if (
+            workers > 1
+            and self.comm is None
+            and os.environ.get("PSGD_B200_COMM", "p2p") == "p2p"
+            and 2 * workers * total * 4 <= self.P2P_ARENA_LIMIT_BYTES
+        ):
+            from .parallel.symm import Channel
+
+            self.comm = Channel(total)
 
     def _launch(self, mode: int, hyper_dev: torch.Tensor, divisor: float) -> None:
         code = self.lib.psgd_flat_launch(
@@ -448,6 +482,7 @@ class NativeFlatAllReduce:
             _ptr(hyper_dev),
             _ptr(self._flat),
             float(divisor),
+            self.comm.ptr if self.comm is not None else ctypes.c_void_p(0),
             _stream_ptr(),
         )
         native.check(code, "psgd_flat_launch")
@@ -459,6 +494,9 @@ class NativeFlatAllReduce:
         workers = world_size()
         if workers == 1:
             self._launch(3, self._hyper_dev, 1.0)
+        elif self.comm is not None:
+            self._launch(5, self._hyper_dev, float(workers))
+            self._launch(6, self._hyper_dev, 1.0)
         else:
             self._launch(0, self._hyper_dev, float(workers))
             dist.all_reduce(self._flat)
@@ -471,6 +509,9 @@ class NativeFlatAllReduce:
         workers = world_size()
         if workers == 1:
             self._launch(4, hyper_dev, 1.0)
+        elif self.comm is not None:
+            self._launch(5, hyper_dev, float(workers))
+            self._launch(7, hyper_dev, 1.0)
         else:
             self._launch(0, hyper_dev, float(workers))
             dist.all_reduce(self._flat)

@@ -23,7 +23,7 @@ def declare(lib) -> None:
     lib.psgd_gemm_template_rank.restype = i32
     lib.psgd_gemm_template_rank.argtypes = [i32]
     lib.psgd_gemm_ffma_launch.restype = i32
-    lib.psgd_gemm_ffma_launch.argtypes = [i32, i32, i32, vp, vp, i32, vp, vp, i32, vp, vp, vp, vp, vp]
+    lib.psgd_gemm_ffma_launch.argtypes = [i32, i32, i32, vp, vp, i32, vp, vp, i32, vp, vp, vp, vp, vp, i32, vp]
 
     lib.psgd_finalize_launch.restype = i32
     lib.psgd_finalize_launch.argtypes = [i32, vp, vp, i32, vp, i32, vp, vp, vp, vp, f32, i32, vp]
@@ -31,7 +31,7 @@ def declare(lib) -> None:
     lib.psgd_flat_block_elems.restype = i32
     lib.psgd_flat_block_elems.argtypes = []
     lib.psgd_flat_launch.restype = i32
-    lib.psgd_flat_launch.argtypes = [i32, vp, vp, vp, i32, vp, vp, f32, vp]
+    lib.psgd_flat_launch.argtypes = [i32, vp, vp, vp, i32, vp, vp, f32, vp, vp]
 
     for name, sig in _OPTIONAL.items():
         fn = getattr(lib, name, None)
@@ -45,4 +45,16 @@ _OPTIONAL = {
     "psgd_sign_pack": (i32, [vp, i64, vp, vp]),
     "psgd_sign_unpack": (i32, [vp, i64, f32, vp, i32, vp]),
     "psgd_sign_vote": (i32, [vp, i32, i64, i32, vp, vp, vp]),
+    "psgd_symm_alloc": (i32, [C.c_size_t, C.POINTER(vp)]),
+    "psgd_symm_free": (i32, [vp]),
+    "psgd_symm_handle_bytes": (i32, []),
+    "psgd_symm_export": (i32, [vp, vp]),
+    "psgd_symm_import": (i32, [vp, C.POINTER(vp)]),
+    "psgd_symm_unmap": (i32, [vp]),
+    "psgd_status_alloc": (i32, [C.POINTER(C.POINTER(i32)), C.POINTER(C.POINTER(i32))]),
+    "psgd_status_free": (i32, [C.POINTER(i32)]),
+    "psgd_comm_desc_bytes": (i32, []),
+    "psgd_comm_fill": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, i64, C.c_double]),
+    "psgd_factor_reduce_launch": (i32, [vp, i64, vp, vp, vp]),
+    "psgd_allreduce_oneshot_launch": (i32, [vp, vp, vp, i64, f32, i32, vp]),
 }

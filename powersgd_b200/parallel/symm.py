@@ -1,0 +1,161 @@
+"""Symmetric memory and in-kernel collective channels over NVLink peer mappings.
+
+`Channel` is the host-side handle of one stream of collectives (csrc/psgd_comm.cuh): it
+allocates this rank's slot arena and flag pad, exchanges CUDA-IPC handles with the other
+ranks once (through the existing torch.distributed group — the only use of a library
+collective), maps every peer's arena, and uploads the device descriptor that kernels take.
+
+Failure handling: device-side waits are bounded (`timeout_ms`, default from
+PSGD_B200_COMM_TIMEOUT_MS or 20 s). A wait that runs out writes a status word in mapped
+pinned memory; `check()` turns it into `PowerSGDCommTimeout` on the host without touching
+the GPU. The reference has no equivalent (its NCCL all-reduce simply blocks,
+powersgd/powersgd.py:205-209).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+
+MAX_WORLD = 8
+
+
+class PowerSGDCommTimeout(RuntimeError):
+    """A bounded device-side wait on a peer ran out."""
+
+
+def _vp(x: int) -> ctypes.c_void_p:
+    return ctypes.c_void_p(int(x))
+
+
+def default_timeout_ms() -> float:
+    return float(os.environ.get("PSGD_B200_COMM_TIMEOUT_MS", "20000"))
+
+
+class SymmetricBuffer:
+    """`nbytes` of zeroed device memory on every rank, each rank's copy mapped on all others."""
+
+    def __init__(self, nbytes: int, group=None):
+        self.lib = native.lib()
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.nbytes = int(nbytes)
+        local = ctypes.c_void_p()
+        native.check(self.lib.psgd_symm_alloc(ctypes.c_size_t(self.nbytes), ctypes.byref(local)), "psgd_symm_alloc")
+        self.local = int(local.value)
+        hb = self.lib.psgd_symm_handle_bytes()
+        handle = (ctypes.c_ubyte * hb)()
+        native.check(self.lib.psgd_symm_export(_vp(self.local), handle), "psgd_symm_export")
+        gathered: List[Optional[bytes]] = [None] * self.world
+        dist.all_gather_object(gathered, bytes(handle), group=group)
+        self.ptrs: List[int] = []
+        self._imported: List[int] = []
+        for r, blob in enumerate(gathered):
+            if r == self.rank:
+                self.ptrs.append(self.local)
+                continue
+            buf = (ctypes.c_ubyte * hb).from_buffer_copy(blob)
+            mapped = ctypes.c_void_p()
+            native.check(self.lib.psgd_symm_import(buf, ctypes.byref(mapped)), "psgd_symm_import")
+            self.ptrs.append(int(mapped.value))
+            self._imported.append(int(mapped.value))
+        dist.barrier(group=group)
+
+    def close(self) -> None:
+        if self.local == 0:
+            return
+        torch.cuda.synchronize()
+        for p in self._imported:
+            self.lib.psgd_symm_unmap(_vp(p))
+        self._imported = []
+        if dist.is_initialized():
+            try:
+                dist.barrier(group=self.group)
+            except Exception:
+                pass
+        self.lib.psgd_symm_free(_vp(self.local))
+        self.local = 0
+
+
+class Channel:
+    """One ordered stream of in-kernel collectives with `cap` floats per rank per message."""
+
+    def __init__(self, cap_floats: int, group=None, timeout_ms: Optional[float] = None):
+        if not (dist.is_available() and dist.is_initialized()):
+            raise RuntimeError("Channel needs an initialised torch.distributed process group")
+        self.lib = native.lib()
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > MAX_WORLD:
+            raise ValueError(f"in-kernel collectives support up to {MAX_WORLD} ranks on one NVSwitch domain")
+        self.cap = max(int(cap_floats), 1)
+        self.timeout_ms = default_timeout_ms() if timeout_ms is None else float(timeout_ms)
+        device = torch.device("cuda", torch.cuda.current_device())
+        self.device = device
+        self.slots = SymmetricBuffer(2 * self.world * self.cap * 4, group)
+        self.flags = SymmetricBuffer(256, group)
+        # local bookkeeping words: epoch, arrival counters
+        self._words = torch.zeros(16, dtype=torch.int32, device=device)
+        host_ptr, dev_ptr = ctypes.POINTER(ctypes.c_int)(), ctypes.POINTER(ctypes.c_int)()
+        native.check(self.lib.psgd_status_alloc(ctypes.byref(host_ptr), ctypes.byref(dev_ptr)), "psgd_status_alloc")
+        self._status_host = host_ptr
+        self._status_dev = ctypes.cast(dev_ptr, ctypes.c_void_p).value
+        nbytes = self.lib.psgd_comm_desc_bytes()
+        host_desc = (ctypes.c_ubyte * nbytes)()
+        slots = (ctypes.c_void_p * self.world)(*self.slots.ptrs)
+        flags = (ctypes.c_void_p * self.world)(*self.flags.ptrs)
+        base = self._words.data_ptr()
+        native.check(
+            self.lib.psgd_comm_fill(
+                host_desc, self.world, self.rank, slots, flags, _vp(base), _vp(base + 16), _vp(self._status_dev),
+                ctypes.c_longlong(self.cap), ctypes.c_double(self.timeout_ms),
+            ),
+            "psgd_comm_fill",
+        )
+        self.desc = torch.frombuffer(bytearray(bytes(host_desc)), dtype=torch.uint8).to(device)
+        torch.cuda.synchronize()
+
+    @property
+    def ptr(self) -> ctypes.c_void_p:
+        return _vp(self.desc.data_ptr())
+
+    @property
+    def status(self) -> int:
+        return int(self._status_host[0])
+
+    def check(self) -> None:
+        code = self.status
+        if code != 0:
+            raise PowerSGDCommTimeout(
+                f"rank {self.rank}: a device-side wait on a peer gave up after {self.timeout_ms:.0f} ms (status {code})"
+            )
+
+    def reset_status(self) -> None:
+        self._status_host[0] = 0
+
+    def all_reduce_(self, tensor: torch.Tensor, scale: float = 1.0, max_blocks: int = 128) -> torch.Tensor:
+        """In-place one-launch SUM all-reduce (times `scale`) of a contiguous float32 tensor."""
+        if tensor.numel() > self.cap:
+            raise ValueError(f"message of {tensor.numel()} floats exceeds the channel capacity {self.cap}")
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        native.check(
+            self.lib.psgd_allreduce_oneshot_launch(
+                self.ptr, _vp(tensor.data_ptr()), _vp(tensor.data_ptr()), ctypes.c_longlong(tensor.numel()),
+                ctypes.c_float(scale), max_blocks, stream,
+            ),
+            "psgd_allreduce_oneshot_launch",
+        )
+        return tensor
+
+    def close(self) -> None:
+        self.slots.close()
+        self.flags.close()
+        if self._status_host:
+            self.lib.psgd_status_free(self._status_host)
+            self._status_host = None

@@ -1,0 +1,262 @@
+"""Multi-rank scenarios, run as `python -m torch.distributed.run ... tests/dist_worker.py NAME`.
+
+Every scenario prints `SCENARIO-OK` on rank 0 when its checks pass; the pytest wrappers look
+for that line. Device scenarios use NCCL (one rank per GPU); host scenarios use gloo.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def _init(backend):
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    if backend == "nccl":
+        local = int(os.environ.get("LOCAL_RANK", rank))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return rank, world, torch.device("cuda", local)
+    dist.init_process_group("gloo")
+    return rank, world, torch.device("cpu")
+
+
+def _same_on_all_ranks(t, world):
+    gathered = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(gathered, t.contiguous())
+    return all(torch.equal(gathered[0], g) for g in gathered)
+
+
+def _rel(a, b):
+    return ((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-30)).item()
+
+
+# ------------------------------------------------------------------------------------------
+def scenario_channel_allreduce():
+    rank, world, dev = _init("nccl")
+    from powersgd_b200.parallel.symm import Channel
+
+    ch = Channel(1 << 20, timeout_ms=5000)
+    for it, n in enumerate([1, 7, 1000, 4097, 1 << 16, 1 << 20, 333]):
+        g = torch.Generator(device="cpu").manual_seed(100 * it + rank)
+        x = torch.randn(n, generator=g).to(dev)
+        ref = x.clone()
+        dist.all_reduce(ref)
+        ch.all_reduce_(x)
+        torch.cuda.synchronize()
+        ch.check()
+        assert _rel(x, ref) < 1e-6, (n, _rel(x, ref))
+        assert _same_on_all_ranks(x, world)
+    # back-to-back launches without host synchronisation (epoch / double-buffer logic)
+    x = torch.full((5000,), float(rank + 1), device=dev)
+    for _ in range(50):
+        ch.all_reduce_(x, scale=1.0 / world)
+    torch.cuda.synchronize()
+    ch.check()
+    expect = sum(range(1, world + 1)) / world
+    assert torch.allclose(x, torch.full_like(x, expect), rtol=1e-5), x[:4]
+    dist.barrier()
+    ch.close()
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
+def scenario_channel_timeout():
+    """One rank stays away from a collective: the others' bounded waits give up, the kernels
+    drain, the status word is set and the context stays usable."""
+    rank, world, dev = _init("nccl")
+    from powersgd_b200.parallel.symm import Channel, PowerSGDCommTimeout
+
+    ch = Channel(4096, timeout_ms=300)
+    x = torch.ones(1024, device=dev)
+    raised = False
+    if rank != world - 1:
+        ch.all_reduce_(x)
+        torch.cuda.synchronize()
+        try:
+            ch.check()
+        except PowerSGDCommTimeout:
+            raised = True
+        assert raised, "expected a timeout status"
+        # the device is still healthy
+        y = torch.arange(10, device=dev).sum().item()
+        assert y == 45
+    dist.barrier()
+    ch.close()
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
+def scenario_powersgd_native():
+    rank, world, dev = _init("nccl")
+    from powersgd_b200 import Config, PowerSGD
+
+    shapes = [(64, 3, 3, 3), (64, 64, 3, 3), (64, 64, 3, 3), (10, 512), (130, 650), (64,), (10,), (300, 1200)]
+    params = [torch.zeros(s, device=dev) for s in shapes]
+    cfg = Config(rank=2, min_compression_rate=2, num_iters_per_step=2, start_compressing_after_num_steps=1)
+    ours = PowerSGD(params, cfg, backend="native")
+    oracle = PowerSGD(params, cfg, backend="torch")
+    g = torch.Generator().manual_seed(rank)
+    ga = [torch.randn(s, generator=g).to(dev) for s in shapes]
+    gb = [x.clone() for x in ga]
+    for step in range(4):
+        mean_in = [x.clone() for x in ga]
+        for x in mean_in:
+            dist.all_reduce(x)
+            x.div_(world)
+        oa = [o.clone() for o in ours.aggregate(ga)]
+        ob = oracle.aggregate(gb)
+        torch.cuda.synchronize()
+        for x, y in zip(oa, ob):
+            assert _rel(x, y) < 5e-5, (step, x.shape, _rel(x, y))
+            assert _same_on_all_ranks(x, world), "outputs differ between ranks"
+        for x, y, keep in zip(ga, gb, ours.is_compressed_mask):
+            if keep:
+                assert _rel(x, y) < 5e-5
+        # mean_i(residual_i) + output == mean_i(input_i)
+        for res, out, m in zip(ga, oa, mean_in):
+            r = res.clone()
+            dist.all_reduce(r)
+            r.div_(world)
+            assert _rel(r + out, m) < 1e-5
+        assert _same_on_all_ranks(ours._powersgd._ps_buffer, world)
+        assert _same_on_all_ranks(ours._powersgd._qs_buffer, world)
+        noise = [torch.randn(s, generator=g).to(dev) for s in shapes]
+        for x, y, z in zip(ga, gb, noise):
+            x.add_(z)
+            y.add_(z)
+    comm = ours._powersgd._native.comm
+    assert comm is not None, "expected the in-kernel all-reduce path"
+    comm.check()
+    dist.barrier()
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
+def scenario_train_step_graph():
+    rank, world, dev = _init("nccl")
+    from powersgd_b200 import Config, PowerSGD
+    from powersgd_b200.engine import TrainStep
+    from powersgd_b200.models import ResNet18
+
+    torch.manual_seed(0)
+    model = ResNet18().to(dev)
+    params = list(model.parameters())
+    opt = torch.optim.SGD(params, lr=0.05, momentum=0.9, nesterov=True, weight_decay=1e-4)
+    agg = PowerSGD(params, Config(rank=2, num_iters_per_step=2, start_compressing_after_num_steps=0))
+    step = TrainStep(model, torch.nn.functional.cross_entropy, opt, agg, cuda_graph=True)
+    g = torch.Generator().manual_seed(10 + rank)
+    losses = []
+    for i in range(8):
+        x = torch.randn(32, 3, 32, 32, generator=g).to(dev)
+        y = torch.randint(0, 10, (32,), generator=g).to(dev)
+        losses.append(float(step(x, y).item()))
+    torch.cuda.synchronize()
+    assert step._graphs, "the step was never captured"
+    assert all(l == l for l in losses), losses
+    for p in params:
+        assert _same_on_all_ranks(p.detach(), world), "replicas drifted"
+    dist.barrier()
+    if rank == 0:
+        print("SCENARIO-OK", losses[0], losses[-1])
+
+
+def scenario_mlp_gloo():
+    """BASELINE config 1: 2-layer MLP on CPU ranks; parameters stay bit-identical."""
+    rank, world, dev = _init("gloo")
+    from powersgd_b200 import Config, PowerSGD, optimizer_step
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(784, 256), torch.nn.ReLU(), torch.nn.Linear(256, 10))
+    params = list(model.parameters())
+    opt = torch.optim.SGD(params, lr=0.1, momentum=0.9)
+    agg = PowerSGD(params, Config(rank=1, min_compression_rate=10, num_iters_per_step=2, start_compressing_after_num_steps=0))
+    assert agg.is_compressed_mask == [True, False, False, False]
+    g = torch.Generator().manual_seed(1 + rank)
+    first = last = None
+    for step in range(20):
+        x = torch.randn(64, 784, generator=g)
+        y = torch.randint(0, 10, (64,), generator=g)
+        loss = torch.nn.functional.cross_entropy(model(x), y)
+        loss.backward()
+        optimizer_step(opt, agg)
+        first = loss.item() if first is None else first
+        last = loss.item()
+    for p in params:
+        assert _same_on_all_ranks(p.detach(), world)
+    assert _same_on_all_ranks(agg._powersgd._ps_buffer, world)
+    dist.barrier()
+    if rank == 0:
+        print("SCENARIO-OK", first, last)
+
+
+def scenario_ef_identity_gloo():
+    rank, world, dev = _init("gloo")
+    from powersgd_b200 import Config, PowerSGD
+    from powersgd_b200.ops.emulate import emulated_aggregate
+
+    shapes = [(20, 30), (20, 30), (16, 3, 3, 3), (7,)]
+    params = [torch.zeros(s) for s in shapes]
+    agg = PowerSGD(params, Config(rank=2, min_compression_rate=1.5, num_iters_per_step=3, start_compressing_after_num_steps=0))
+    g = torch.Generator().manual_seed(rank)
+    grads = [torch.randn(s, generator=g) for s in shapes]
+    mean_in = [x.clone() for x in grads]
+    for x in mean_in:
+        dist.all_reduce(x)
+        x.div_(world)
+    # the kernel pipeline's algebra, with a gloo all-reduce in place of the peer pushes
+    core = agg._powersgd
+    twin = [x.clone() for x, keep in zip(grads, agg.is_compressed_mask) if keep]
+    import copy
+
+    core_twin = copy.deepcopy(core)
+    out_twin = emulated_aggregate(core_twin, twin, allreduce=dist.all_reduce)
+    out = agg.aggregate(grads)
+    k = 0
+    for o, keep in zip(out, agg.is_compressed_mask):
+        if keep:
+            assert _rel(out_twin[k], o) < 1e-4, _rel(out_twin[k], o)
+            k += 1
+    for o, res, m in zip(out, grads, mean_in):
+        assert _same_on_all_ranks(o, world)
+        r = res.clone()
+        dist.all_reduce(r)
+        r.div_(world)
+        assert torch.allclose(r + o, m, atol=1e-5)
+    dist.barrier()
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
+def scenario_rank_failure_gloo():
+    """A rank that raises before a collective: the others' next collective ends with an error
+    (short process-group timeout) instead of hanging."""
+    import datetime
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=3))
+    from powersgd_b200 import AllReduce
+
+    ok = AllReduce().aggregate([torch.ones(4)])
+    assert torch.allclose(ok[0], torch.ones(4))
+    if rank == world - 1:
+        print("SCENARIO-OK-FAILING-RANK-LEFT")
+        os._exit(0)  # leaves between steps, nothing in flight
+    failed = False
+    try:
+        AllReduce().aggregate([torch.ones(4)])
+    except Exception:
+        failed = True
+    assert failed, "expected the collective to fail once a rank is gone"
+    if rank == 0:
+        print("SCENARIO-OK")
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    globals()["scenario_" + sys.argv[1]]()
+    if dist.is_initialized():
+        dist.destroy_process_group()
