@@ -1,0 +1,178 @@
+#!/usr/bin/env python3
+"""Compression micro-benchmark (BASELINE config 2).
+
+For float32 gradient matrices of the named shapes — each drawn as a rank-8 product of N(0,1)
+factors plus N(0, 1e-3) noise — time one `aggregate()` (compress + reduce + decompress +
+error feedback) of this library's native kernels against
+
+  * the reference formulation (batched `torch.bmm` / `torch.linalg.qr` + NCCL all-reduce; the
+    unmodified upstream package when it is installed under baseline/_ref, else this
+    repository's PyTorch restatement of it), and
+  * an uncompressed all-reduce of the same gradients (multi-GPU runs),
+
+and report the relative compression error of both. Device-timed with CUDA events per
+iteration after warm-up, max over ranks; a buffer larger than L2 is rewritten between timed
+iterations when the gradients themselves are smaller than L2.
+
+    python bench_compress.py --shapes 1024x1024,4096x1024 --ranks 1,4 --iters 2 --batch 4
+    python -m torch.distributed.run --nproc-per-node 2 ... bench_compress.py ...
+
+One JSON line per (shape, rank, iters) on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 << 20
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default="1024x1024,4096x1024,4096x4096,50257x1024")
+    ap.add_argument("--ranks", default="1,2,4,8,16")
+    ap.add_argument("--iters", default="1,2")
+    ap.add_argument("--batch", type=int, default=4, help="matrices per shape (one shape group)")
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--skip-reference", action="store_true")
+    ap.add_argument("--only-ours", action="store_true", help="time only the native path (used for profiler captures)")
+    return ap.parse_args()
+
+
+def make_gradients(n, m, batch, device, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    out = []
+    for _ in range(batch):
+        a = torch.randn(n, 8, generator=g).to(device) @ torch.randn(8, m, generator=g).to(device)
+        a.add_(torch.randn(n, m, generator=g).to(device), alpha=1e-3 ** 0.5)
+        out.append(a)
+    return out
+
+
+def reference_module():
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if os.path.isdir(os.path.join(ref_root, "powersgd")):
+        sys.path.insert(0, ref_root)
+        import powersgd
+
+        return powersgd
+    return None
+
+
+def time_aggregate(make_agg, grads, steps, warmup, flush, world, device):
+    agg = make_agg()
+    work = [g.clone() for g in grads]
+    times = []
+    out = None
+    for i in range(warmup + steps):
+        for w, g in zip(work, grads):
+            w.copy_(g)  # same input every iteration: the timing does not depend on the residual
+        if flush is not None:
+            flush.add_(1.0)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        out = agg.aggregate(work)
+        b.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(a.elapsed_time(b))
+    ms = sum(times) / len(times)
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    err = sum(float(w.double().norm() ** 2) for w in work) ** 0.5
+    return ms, err, out
+
+
+def main():
+    args = parse()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    from powersgd_b200 import BasicConfig, BasicPowerSGD
+
+    ref = None if (args.skip_reference or args.only_ours) else reference_module()
+    peaks = {}
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        with open(peaks_path) as fp:
+            peaks = json.load(fp)
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    hbm_label = "of measured" if peaks else "of fallback"
+
+    for shape in args.shapes.split(","):
+        n, m = (int(v) for v in shape.lower().split("x"))
+        grads = make_gradients(n, m, args.batch, device, seed=1 + rank)
+        nbytes = 4 * n * m * args.batch
+        flush = torch.zeros(2 * L2_BYTES // 4, device=device) if nbytes < 2 * L2_BYTES else None
+        norm_in = sum(float(g.double().norm() ** 2) for g in grads) ** 0.5
+        for r in (int(v) for v in args.ranks.split(",")):
+            for iters in (int(v) for v in args.iters.split(",")):
+                cfg = BasicConfig(rank=r, num_iters_per_step=iters)
+                ours_ms, ours_err, _ = time_aggregate(
+                    lambda: BasicPowerSGD(grads, cfg, backend="native"), grads, args.steps, args.warmup, flush, world, device
+                )
+                row = {
+                    "shape": [n, m], "batch": args.batch, "rank": r, "iters": iters, "n_gpus": world,
+                    "ours_ms": ours_ms, "ours_rel_error": ours_err / norm_in,
+                    "l2": "flush between iterations" if flush is not None else "inputs larger than L2",
+                }
+                # algorithmic traffic: `iters` reads of M, then read M + write residual + write update
+                traffic = (iters + 3) * nbytes
+                row["ours_gbs"] = traffic / (ours_ms * 1e-3) / 1e9
+                row["ours_hbm_fraction"] = f"{row['ours_gbs'] / hbm:.3f} {hbm_label} {hbm:.0f} GB/s"
+                if not args.only_ours:
+                    if ref is not None:
+                        make_ref = lambda: ref.powersgd.BasicPowerSGD(grads, ref.powersgd.BasicConfig(rank=r, num_iters_per_step=iters))  # noqa: E731
+                        label = "upstream package"
+                    else:
+                        make_ref = lambda: BasicPowerSGD(grads, cfg, backend="torch")  # noqa: E731
+                        label = "PyTorch restatement"
+                    ref_ms, ref_err, _ = time_aggregate(make_ref, grads, args.steps, args.warmup, flush, world, device)
+                    row.update({"reference_ms": ref_ms, "reference_rel_error": ref_err / norm_in, "reference_impl": label,
+                                "speedup": ref_ms / ours_ms,
+                                "rel_error_gap": abs(ours_err - ref_err) / max(ref_err, 1e-30)})
+                    if world > 1:
+                        flat = torch.cat([g.reshape(-1) for g in grads])
+                        ts = []
+                        for i in range(args.warmup + args.steps):
+                            dist.barrier()
+                            torch.cuda.synchronize()
+                            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                            a.record()
+                            dist.all_reduce(flat)
+                            b.record()
+                            torch.cuda.synchronize()
+                            if i >= args.warmup:
+                                ts.append(a.elapsed_time(b))
+                        t = torch.tensor([sum(ts) / len(ts)], device=device, dtype=torch.float64)
+                        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                        row["uncompressed_allreduce_ms"] = float(t.item())
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+        del grads, flush
+        torch.cuda.empty_cache()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
