@@ -84,21 +84,45 @@ class TilePlan:
         self.nt_rows = min(nt_rows_cap, 128 if self.total_elems < (64 << 20) else 256)
         self.nn_rows = lib.psgd_gemm_nn_tile_rows(self.max_r)
         self.nn_cols_cap = 1024
+        self.rp_tc = lib.psgd_gemm_tc_rank_pad(self.max_r)
 
     def vec_ok(self, mi: int) -> bool:
         g = self.plan.groups[self.mats[mi][0]]
         return g.m % 4 == 0
 
-    def build(self, vec_flags: Sequence[bool]):
-        """Tile arrays split by vector width. Returns dict name -> {4: array, 1: array}."""
-        nt = {4: [], 1: []}
-        nn = {4: [], 1: []}
+    def build(self, vec_flags: Sequence[bool], tc_flags: Optional[Sequence[bool]] = None):
+        """Tile arrays split by vector width (CUDA-core kernels: keys 4 and 1) and, for the
+        matrices flagged in `tc_flags`, tensor-core tiles (key "tc")."""
+        nt = {4: [], 1: [], "tc": []}
+        nn = {4: [], 1: [], "tc": []}
         fin = {4: [], 1: []}
         ticket = 0
-        nt_slots = nn_slots = 0
+        nt_slots = nn_slots = tc_slots = 0
+        tc_flags = tc_flags or [False] * len(self.mats)
+        n_tc_elems = sum(self.plan.groups[gi].n * self.plan.groups[gi].m for (gi, _p, _i), f in zip(self.mats, tc_flags) if f)
+        # K extent of one tensor-core tile: long enough to amortise the pipeline ramp, short
+        # enough that a small model still fills the GPU
+        tc_k = 1024 if n_tc_elems >= (32 << 20) else (512 if n_tc_elems >= (8 << 20) else 256)
         for mi, (gi, _pos, _idx) in enumerate(self.mats):
             g = self.plan.groups[gi]
             v = 4 if vec_flags[mi] else 1
+            for r0 in range(0, g.n, 32):
+                for c0 in range(0, g.m, 128):
+                    fin[v].append((mi, r0, min(32, g.n - r0), c0, min(128, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
+            if tc_flags[mi]:
+                row_blocks = _split_even(g.n, tc_k, 32)
+                for c0 in range(0, g.m, 128):
+                    for si, (r0, rows) in enumerate(row_blocks):
+                        nt["tc"].append((mi, r0, rows, c0, min(128, g.m - c0), si, len(row_blocks), ticket, tc_slots, (0, 0, 0)))
+                    ticket += 1
+                    tc_slots += len(row_blocks)
+                col_blocks = _split_even(g.m, tc_k, 32)
+                for r0 in range(0, g.n, 128):
+                    for si, (c0, cols) in enumerate(col_blocks):
+                        nn["tc"].append((mi, r0, min(128, g.n - r0), c0, cols, si, len(col_blocks), ticket, tc_slots, (0, 0, 0)))
+                    ticket += 1
+                    tc_slots += len(col_blocks)
+                continue
             row_blocks = _split_even(g.n, self.nt_rows, 1)
             for c0 in range(0, g.m, 128):
                 cols = min(128, g.m - c0)
@@ -113,11 +137,9 @@ class TilePlan:
                     nn[v].append((mi, r0, rows, c0, cols, si, len(col_blocks), ticket, nn_slots, (0, 0, 0)))
                 ticket += 1
                 nn_slots += len(col_blocks)
-            for r0 in range(0, g.n, 32):
-                for c0 in range(0, g.m, 128):
-                    fin[v].append((mi, r0, min(32, g.n - r0), c0, min(128, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
         self.n_tickets = max(ticket, 1)
         self.partial_floats = max(nt_slots * 128 * self.rt, nn_slots * self.nn_rows * self.rt, 1)
+        self.partial_tc_floats = max(tc_slots * 128 * self.rp_tc, 1)
 
         def arr(items):
             return np.array(items, dtype=layout.TILE_DTYPE) if items else np.zeros(0, dtype=layout.TILE_DTYPE)
@@ -236,13 +258,33 @@ class NativeCompressor:
             vec.append(g.m % 4 == 0 and all(p % 16 == 0 for p in ptrs))
         assert where is not None
         self._mats_dev = _to_device(descs, self.device)
-        tile_arrays = self.tiles.build(vec)
+        # tensor-core (TMA + tcgen05) path: matrices TMA can address and that are worth it
+        mode = os.environ.get("PSGD_B200_GEMM", "auto")
+        hbm_bound = self.tiles.total_elems * 4 > (96 << 20)
+        tc = []
+        maps = np.zeros((len(self.tiles.mats), 256), dtype=np.uint8)
+        for mi, (gi, _pos, idx) in enumerate(self.tiles.mats):
+            g = self.plan.groups[gi]
+            ok = vec[mi] and g.n >= 128 and g.m >= 128 and mode != "ffma"
+            ok = ok and (mode == "tc" or hbm_bound or self.tiles.max_r >= 8)
+            if ok:
+                buf = (ctypes.c_ubyte * 256)()
+                code = self.lib.psgd_tma_encode_matrix(buf, ctypes.c_void_p(grads[idx].data_ptr()), g.n, g.m)
+                native.check(code, "psgd_tma_encode_matrix")
+                maps[mi] = np.frombuffer(buf, dtype=np.uint8)
+            tc.append(bool(ok))
+        self._maps_dev = _to_device(maps, self.device)
+        self._tc_split = os.environ.get("PSGD_B200_TC_PRECISION", "split") != "tf32"
+        self.uses_tensor_cores = any(tc)
+        tile_arrays = self.tiles.build(vec, tc)
         self._tiles_dev: Dict[str, Dict[int, Tuple[torch.Tensor, int]]] = {}
         for name, by_vec in tile_arrays.items():
             self._tiles_dev[name] = {
                 v: (_to_device(a, self.device) if len(a) else None, len(a)) for v, a in by_vec.items()
             }
         self._partial = torch.empty(self.tiles.partial_floats, device=self.device, dtype=torch.float32)
+        self._partial_tc = torch.empty(self.tiles.partial_tc_floats, device=self.device, dtype=torch.float32)
+        self._tc_status = torch.zeros(1, device=self.device, dtype=torch.int32)
         self._tickets = torch.zeros(self.tiles.n_tickets, device=self.device, dtype=torch.int32)
         self._out_views = out_views
         self._key = key
@@ -265,7 +307,31 @@ class NativeCompressor:
 
     def _gemm(self, transposed: bool, fin: torch.Tensor, fout: torch.Tensor, corr_fac, corr_c):
         name = "nt" if transposed else "nn"
-        expected = sum(self._tiles_dev[name][v][1] for v in (4, 1))
+        expected = sum(self._tiles_dev[name][v][1] for v in (4, 1, "tc"))
+        tiles, count = self._tiles_dev[name]["tc"]
+        if count:
+            code = self.lib.psgd_gemm_tc_launch(
+                1 if transposed else 0,
+                1 if self._tc_split else 0,
+                self.tiles.max_r,
+                _ptr(self._mats_dev),
+                _ptr(tiles),
+                count,
+                _ptr(self._maps_dev),
+                _ptr(fin),
+                _ptr(fout),
+                len(corr_fac),
+                ctypes.cast(_ptr_array(corr_fac), ctypes.c_void_p),
+                ctypes.cast(_ptr_array(corr_c), ctypes.c_void_p),
+                _ptr(self._partial_tc),
+                _ptr(self._tickets),
+                self.comm.ptr if self.comm is not None else ctypes.c_void_p(0),
+                expected,
+                _ptr(self._tc_status),
+                _stream_ptr(),
+            )
+            native.check(code, "psgd_gemm_tc_launch")
+            self.launches += 1
         for v in (4, 1):
             tiles, count = self._tiles_dev[name][v]
             if count == 0:

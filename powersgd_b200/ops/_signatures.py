@@ -45,6 +45,9 @@ _OPTIONAL = {
     "psgd_sign_pack": (i32, [vp, i64, vp, vp]),
     "psgd_sign_unpack": (i32, [vp, i64, f32, vp, i32, vp]),
     "psgd_sign_vote": (i32, [vp, i32, i64, i32, vp, vp, vp]),
+    "psgd_gemm_tc_rank_pad": (i32, [i32]),
+    "psgd_tma_encode_matrix": (i32, [vp, vp, i32, i32]),
+    "psgd_gemm_tc_launch": (i32, [i32, i32, i32, vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, vp, vp]),
     "psgd_symm_alloc": (i32, [C.c_size_t, C.POINTER(vp)]),
     "psgd_symm_free": (i32, [vp]),
     "psgd_symm_handle_bytes": (i32, []),
