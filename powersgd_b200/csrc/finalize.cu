@@ -45,7 +45,9 @@ __device__ __forceinline__ float psgd_sgd_update(float g, float& p, float* mom_p
   return p;
 }
 
-template <int VEC>
+// SAME: one worker, so the summed factors ARE the local ones and the update equals what is
+// removed from the gradient: one accumulator, half the shared-memory traffic and FMAs.
+template <int VEC, bool SAME>
 __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs a) {
   const PsgdTile t = a.tiles[blockIdx.x];
   const PsgdMat mt = a.mats[t.mat];
@@ -75,10 +77,10 @@ __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs
         const int k = k0 + kk, h = k / r, j = k % r;
         const long long off = mt.p_off + (long long)(t.row0 + lr) * r + j;
         vl = a.lloc[h][off];
-        vs = a.lsum[h][off];
+        if (!SAME) vs = a.lsum[h][off];
       }
       sLl[kk][lr] = vl;
-      sLs[kk][lr] = vs;
+      if (!SAME) sLs[kk][lr] = vs;
     }
     for (int e = tid; e < FIN_KC * FIN_COLS; e += FIN_THREADS) {
       const int lc = e / FIN_KC, kk = e % FIN_KC;
@@ -87,20 +89,20 @@ __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs
         const int k = k0 + kk, h = k / r, j = k % r;
         const long long off = mt.q_off + (long long)(t.col0 + lc) * r + j;
         vl = a.rloc[h][off];
-        vs = a.rsum[h][off];
+        if (!SAME) vs = a.rsum[h][off];
       }
       // lane-major placement so that each lane's 4 columns are adjacent for VEC == 4
       const int pos = (VEC == 4) ? lc : ((lc & 31) * 4 + (lc >> 5));
       sRl[kk][pos] = vl;
-      sRs[kk][pos] = vs;
+      if (!SAME) sRs[kk][pos] = vs;
     }
     __syncthreads();
 #pragma unroll 4
     for (int kk = 0; kk < kc; ++kk) {
       const float4 ll = *reinterpret_cast<const float4*>(&sLl[kk][warp * 4]);
-      const float4 ls = *reinterpret_cast<const float4*>(&sLs[kk][warp * 4]);
       const float4 rl = *reinterpret_cast<const float4*>(&sRl[kk][lane * 4]);
-      const float4 rs = *reinterpret_cast<const float4*>(&sRs[kk][lane * 4]);
+      const float4 ls = SAME ? ll : *reinterpret_cast<const float4*>(&sLs[kk][warp * 4]);
+      const float4 rs = SAME ? rl : *reinterpret_cast<const float4*>(&sRs[kk][lane * 4]);
       const float lv[4] = {ll.x, ll.y, ll.z, ll.w}, sv[4] = {ls.x, ls.y, ls.z, ls.w};
       const float rlv[4] = {rl.x, rl.y, rl.z, rl.w}, rsv[4] = {rs.x, rs.y, rs.z, rs.w};
 #pragma unroll
@@ -108,11 +110,17 @@ __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           accE[u][c] = fmaf(lv[u], rlv[c], accE[u][c]);
-          accA[u][c] = fmaf(sv[u], rsv[c], accA[u][c]);
+          if (!SAME) accA[u][c] = fmaf(sv[u], rsv[c], accA[u][c]);
         }
     }
   }
 
+  if (SAME) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) accA[u][c] = accE[u][c];
+  }
   const PsgdHyper h = a.hyper[mt.hyper];
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
@@ -122,7 +130,7 @@ __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs
     if (VEC == 4) {
       const int col = t.col0 + lane * 4;
       if (lane * 4 >= t.cols) continue;
-      float4 g = *reinterpret_cast<const float4*>(mt.grad + rowoff + col);
+      const float4 g = *reinterpret_cast<const float4*>(mt.grad + rowoff + col);
       float gv[4] = {g.x, g.y, g.z, g.w};
       float av[4];
 #pragma unroll
@@ -192,8 +200,15 @@ PSGD_API int psgd_finalize_launch(int vec4, const void* mats, const void* tiles,
   }
   a.inv_world = inv_world;
   a.fused_sgd = fused_sgd;
-  if (vec4) psgd_finalize_kernel<4><<<ntiles, FIN_THREADS, 0, stream>>>(a);
-  else psgd_finalize_kernel<1><<<ntiles, FIN_THREADS, 0, stream>>>(a);
+  bool same = true;
+  for (int i = 0; i < nhist; ++i) same = same && lloc[i] == lsum[i] && rloc[i] == rsum[i];
+  if (vec4) {
+    if (same) psgd_finalize_kernel<4, true><<<ntiles, FIN_THREADS, 0, stream>>>(a);
+    else psgd_finalize_kernel<4, false><<<ntiles, FIN_THREADS, 0, stream>>>(a);
+  } else {
+    if (same) psgd_finalize_kernel<1, true><<<ntiles, FIN_THREADS, 0, stream>>>(a);
+    else psgd_finalize_kernel<1, false><<<ntiles, FIN_THREADS, 0, stream>>>(a);
+  }
   PSGD_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -259,9 +259,29 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
   } else {
     // ---------------- converters (then epilogue) ----------------
     const float* __restrict__ fac = a.in + (TRANSPOSED ? mt.p_off : mt.q_off);
+    // each thread stages RP / 4 factor values per stage; they are fetched one stage ahead so
+    // that their L2 latency hides behind the wait for the gradient tile
+    constexpr int PER_THREAD = TC_BK * RP / 128;
+    float pre[PER_THREAD];
+    auto fetch = [&](int kb) {
+      const int k0 = k_begin + kb * TC_BK;
+#pragma unroll
+      for (int i = 0; i < PER_THREAD; ++i) {
+        const int e = tid + i * 128;
+        const int k = e / RP, n = e % RP;
+        float v = 0.f;
+        if (kb < nk && n < r && k0 + k < k_limit && kb * TC_BK + k < k_len) v = __ldg(fac + (long long)(k0 + k) * r + n);
+        pre[i] = v;
+      }
+    };
+    fetch(0);
     for (int kb = 0; kb < nk; ++kb) {
       const int s = kb % TC_STAGES;
       const uint32_t ph = (kb / TC_STAGES) & 1;
+      float cur[PER_THREAD];
+#pragma unroll
+      for (int i = 0; i < PER_THREAD; ++i) cur[i] = pre[i];
+      fetch(kb + 1);
       if (!mbar_wait(&bar_full[s], ph, abort_flag, a.status)) break;
       if (SPLIT) {
         const float4* src = reinterpret_cast<const float4*>(sA + s * TC_A_BYTES);
@@ -274,11 +294,11 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
       }
       // factor slab: B[n][k] for k in this stage, K-major rows of 128 bytes with 128-byte swizzle
       uint8_t* bt = sB + s * B_BYTES;
-      const int k0 = k_begin + kb * TC_BK;
-      for (int e = tid; e < TC_BK * RP; e += 128) {
+#pragma unroll
+      for (int i = 0; i < PER_THREAD; ++i) {
+        const int e = tid + i * 128;
         const int k = e / RP, n = e % RP;
-        float v = 0.f;
-        if (n < r && k0 + k < k_limit && kb * TC_BK + k < k_len) v = __ldg(fac + (long long)(k0 + k) * r + n);
+        const float v = cur[i];
         const float hi = tf32_hi(v);
         const uint32_t off = (uint32_t)(((k >> 2) ^ (n & 7)) << 4) + (uint32_t)(k & 3) * 4u;
         *reinterpret_cast<float*>(bt + n * 128 + off) = hi;

@@ -102,7 +102,7 @@ class TilePlan:
         n_tc_elems = sum(self.plan.groups[gi].n * self.plan.groups[gi].m for (gi, _p, _i), f in zip(self.mats, tc_flags) if f)
         # K extent of one tensor-core tile: long enough to amortise the pipeline ramp, short
         # enough that a small model still fills the GPU
-        tc_k = 1024 if n_tc_elems >= (32 << 20) else (512 if n_tc_elems >= (8 << 20) else 256)
+        tc_k = 512 if n_tc_elems >= (16 << 20) else 256
         for mi, (gi, _pos, _idx) in enumerate(self.mats):
             g = self.plan.groups[gi]
             v = 4 if vec_flags[mi] else 1

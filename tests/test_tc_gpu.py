@@ -18,12 +18,12 @@ def _grads(shapes, dev, seed):
     g = torch.Generator(device="cpu").manual_seed(seed)
     out = []
     for n, m in shapes:
-        a = torch.randn(n, 6, generator=g) @ torch.randn(6, m, generator=g) + 0.1 * torch.randn(n, m, generator=g)
+        a = torch.randn(n, 12, generator=g) @ torch.randn(12, m, generator=g) + 0.1 * torch.randn(n, m, generator=g)
         out.append(a.to(dev))
     return out
 
 
-@pytest.mark.parametrize("rank,iters,precision,tol", [(4, 2, "split", 5e-5), (2, 1, "split", 5e-5), (8, 2, "split", 5e-5),
+@pytest.mark.parametrize("rank,iters,precision,tol", [(4, 2, "split", 5e-5), (2, 1, "split", 5e-5), (8, 2, "split", 2e-4),
                                                        (16, 2, "split", 1e-3), (4, 2, "tf32", 2e-2)])
 def test_tensor_core_products_match_torch_path(monkeypatch, rank, iters, precision, tol):
     monkeypatch.setenv("PSGD_B200_GEMM", "tc")
