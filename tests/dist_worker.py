@@ -256,6 +256,27 @@ def scenario_rank_failure_gloo():
     os._exit(0)
 
 
+def scenario_ddp_hooks_gloo():
+    """The DDP comparison harness with each built-in hook, two CPU ranks."""
+    import datetime
+
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=60))
+    from powersgd_b200.paper import train_ddp
+
+    for hook in ("allreduce", "PowerSGD"):
+        train_ddp.config.update(distributed_backend="gloo", device="cpu", num_epochs=1, max_batches_per_epoch=3,
+                                optimizer_batch_size=8, task_architecture="LeNet", train_size=64, test_size=32,
+                                log_verbosity=0, optimizer_reducer=hook, start_powerSGD_iter=2,
+                                rank=dist.get_rank(), n_workers=dist.get_world_size())
+        task, bits = train_ddp.main()
+        assert bits >= 0
+        for p in task.state:
+            assert torch.isfinite(p).all()
+            assert _same_on_all_ranks(p.detach(), dist.get_world_size())
+    if dist.get_rank() == 0:
+        print("SCENARIO-OK")
+
+
 if __name__ == "__main__":
     globals()["scenario_" + sys.argv[1]]()
     if dist.is_initialized():
