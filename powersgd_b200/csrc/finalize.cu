@@ -228,8 +228,8 @@ struct FlatArgs {
   int mode;  // 0: pack (flat = grad / divisor, grad = 0)
              // 1: unpack (out = flat) ; 2: unpack + SGD on param
              // 3: local (no communication): out = grad / divisor, grad = 0 ; 4: local + SGD
-             // 5: pack + push to every peer's slot, then publish the epoch (in-kernel all-reduce, part 1)
-             // 6: wait for all peers, sum the slots in rank order -> out ; 7: same + SGD (part 2)
+             // 5: pack + push {value, epoch} words to every peer's slot (in-kernel all-reduce, part 1)
+             // 6: poll the own slots, sum them in rank order -> out ; 7: same + SGD (part 2)
   const PsgdCommDev* comm;
 };
 
@@ -245,8 +245,8 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
   if (a.mode >= 5) {
     c = *a.comm;
     e1 = *c.epoch + 1;
-    if (a.mode >= 6) psgd_comm_wait_all(c, e1);
   }
+  bool ok = true;
   for (int e = threadIdx.x; e < FLAT_PER_BLOCK; e += FLAT_THREADS) {
     const long long i = first + e;
     if (i >= it.numel) break;
@@ -258,13 +258,12 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
     } else if (a.mode == 5) {
       const float v = it.grad[i] / a.divisor;
       it.grad[i] = 0.f;
-      for (int p = 0; p < c.world; ++p) psgd_comm_slot(c, p, e1, c.rank)[it.flat_off + i] = v;
+      for (int p = 0; p < c.world; ++p) psgd_comm_store(psgd_comm_slot(c, p, e1, c.rank) + it.flat_off + i, v, e1);
       continue;
     } else if (a.mode == 1 || a.mode == 2) {
       g = a.flat[it.flat_off + i];
     } else if (a.mode >= 6) {
-      g = 0.f;
-      for (int r = 0; r < c.world; ++r) g += __ldcg(psgd_comm_slot(c, c.rank, e1, r) + it.flat_off + i);
+      g = psgd_comm_reduce(c, e1, it.flat_off + i, ok);
     } else {
       g = it.grad[i] / a.divisor;
       it.grad[i] = 0.f;
@@ -279,19 +278,7 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
       it.out[i] = g;
     }
   }
-  if (a.mode >= 5) {
-    // count this CTA in; the last producer publishes, the last consumer closes the epoch
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int* counter = c.arrive + (a.mode == 5 ? 0 : 1);
-      if (psgd_atom_add_acqrel_gpu(counter, 1) == (int)gridDim.x - 1) {
-        *counter = 0;
-        if (a.mode == 5) psgd_comm_publish(c, e1);
-        else *c.epoch = e1;
-      }
-    }
-  }
+  if (a.mode >= 6) psgd_comm_close_epoch(c, e1);  // the last consumer CTA advances the channel
 }
 
 PSGD_API int psgd_flat_block_elems() { return FLAT_PER_BLOCK; }

@@ -34,26 +34,11 @@ struct GemmArgs {
   const float* corr_c[PSGD_MAX_HIST];    // [mat][r*r] cross products
   float* partial;     // scratch for split tiles
   int* tickets;       // arrival counters (all zero between launches)
-  // Multi-GPU: the epilogue also pushes every finished factor row into slot[rank] of every
-  // peer's arena, and the CTA that arrives last (over `expected_ctas`, which may span several
-  // launches of one phase) publishes the next epoch. Null for a single worker.
+  // Multi-GPU: the epilogue also pushes every finished factor element, tagged with the next
+  // epoch, into slot[rank] of every peer's arena. Null for a single worker.
   const PsgdCommDev* comm;
   int expected_ctas;
 };
-
-// Common tail of both product kernels: count this CTA in; the last one publishes.
-__device__ __forceinline__ void gemm_comm_tail(const GemmArgs& a) {
-  if (a.comm == nullptr) return;
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const PsgdCommDev c = *a.comm;
-    if (psgd_atom_add_acqrel_gpu(c.arrive + 0, 1) == a.expected_ctas - 1) {
-      c.arrive[0] = 0;
-      psgd_comm_publish(c, *c.epoch + 1);
-    }
-  }
-}
 
 template <int RT>
 __host__ __device__ constexpr int nt_max_rows() { return RT <= 16 ? NT_MAX_ROWS : NT_MAX_ROWS / 2; }
@@ -167,11 +152,12 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) 
 
   // epilogue: subtract the deflation terms, store Q rows locally and push them to the peers
   float* __restrict__ qout = a.out + mt.q_off;
-  float* push[PSGD_MAX_WORLD];
+  uint2* push[PSGD_MAX_WORLD];
+  int e1 = 0;
   int npush = 0;
   if (a.comm != nullptr && owner) {
     const PsgdCommDev c = *a.comm;
-    const int e1 = *c.epoch + 1;
+    e1 = *c.epoch + 1;
     npush = c.world;
     for (int p = 0; p < PSGD_MAX_WORLD; ++p) push[p] = p < c.world ? psgd_comm_slot(c, p, e1, c.rank) + mt.q_off : nullptr;
   }
@@ -187,9 +173,8 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) 
       s -= d;
     }
     qout[(long long)col * r + k] = s;
-    for (int p = 0; p < npush; ++p) push[p][(long long)col * r + k] = s;
+    for (int p = 0; p < npush; ++p) psgd_comm_store(push[p] + (long long)col * r + k, s, e1);
   }
-  gemm_comm_tail(a);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -291,11 +276,12 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nn_kernel(GemmArgs a) 
   }
 
   float* __restrict__ pout = a.out + mt.p_off;
-  float* push[PSGD_MAX_WORLD];
+  uint2* push[PSGD_MAX_WORLD];
+  int e1 = 0;
   int npush = 0;
   if (a.comm != nullptr && owner) {
     const PsgdCommDev c = *a.comm;
-    const int e1 = *c.epoch + 1;
+    e1 = *c.epoch + 1;
     npush = c.world;
     for (int p = 0; p < PSGD_MAX_WORLD; ++p) push[p] = p < c.world ? psgd_comm_slot(c, p, e1, c.rank) + mt.p_off : nullptr;
   }
@@ -311,9 +297,8 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nn_kernel(GemmArgs a) 
       s -= d;
     }
     pout[(long long)row * r + k] = s;
-    for (int p = 0; p < npush; ++p) push[p][(long long)row * r + k] = s;
+    for (int p = 0; p < npush; ++p) psgd_comm_store(push[p] + (long long)row * r + k, s, e1);
   }
-  gemm_comm_tail(a);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -367,11 +367,11 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
 
   const long long out_off = TRANSPOSED ? mt.q_off : mt.p_off;
   float* __restrict__ fout = a.out + out_off;
-  float* push[PSGD_MAX_WORLD];
-  int npush = 0;
+  uint2* push[PSGD_MAX_WORLD];
+  int npush = 0, e1 = 0;
   if (a.comm != nullptr && owner) {
     const PsgdCommDev c = *a.comm;
-    const int e1 = *c.epoch + 1;
+    e1 = *c.epoch + 1;
     npush = c.world;
     for (int p = 0; p < PSGD_MAX_WORLD; ++p) push[p] = p < c.world ? psgd_comm_slot(c, p, e1, c.rank) + out_off : nullptr;
   }
@@ -387,18 +387,7 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
       s -= dsum;
     }
     fout[row * r + k] = s;
-    for (int p = 0; p < npush; ++p) push[p][row * r + k] = s;
-  }
-  if (a.comm != nullptr) {
-    __threadfence_system();
-    __syncthreads();
-    if (tid == 0) {
-      const PsgdCommDev c = *a.comm;
-      if (psgd_atom_add_acqrel_gpu(c.arrive + 0, 1) == a.expected_ctas - 1) {
-        c.arrive[0] = 0;
-        psgd_comm_publish(c, *c.epoch + 1);
-      }
-    }
+    for (int p = 0; p < npush; ++p) psgd_comm_store(push[p] + row * r + k, s, e1);
   }
 }
 

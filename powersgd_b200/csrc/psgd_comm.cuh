@@ -1,15 +1,17 @@
 // In-kernel collectives over NVLink peer memory: device-side context and primitives.
 //
-// Every rank owns one "slot arena" and one flag pad, allocated with cudaMalloc and mapped into
-// every peer through CUDA IPC. A collective on a channel is:
-//   1. producers STORE their contribution into slot[my_rank] of EVERY peer's arena (pushes are
-//      posted writes; nothing is ever loaded across NVLink on the critical path),
-//   2. the last producer CTA of the launch publishes `epoch` into flag[my_rank] of every peer
-//      (st.release.sys after a system-scope fence),
-//   3. consumers spin (ld.acquire.sys, bounded by %globaltimer) until all W flags show the
-//      epoch, then add the W slots in RANK ORDER, so every rank computes the same bits.
-// Arenas are double buffered by epoch parity: a rank can only start pushing for epoch e+2
-// after it saw every peer's flag for e+1, which a peer raises after it finished consuming e.
+// Every rank owns one "slot arena", allocated with cudaMalloc and mapped into every peer through
+// CUDA IPC. The protocol is flag-in-data (what NCCL calls LL): every float travels as an aligned
+// 8-byte word {value, epoch}. A collective on a channel is
+//   1. producers STORE their contribution into slot[my_rank] of EVERY peer's arena, one 8-byte
+//      store per element (posted writes; nothing is loaded across NVLink, no fences, no flags),
+//   2. consumers poll each word of their OWN arena until its tag equals the epoch, then add the
+//      W slots in RANK ORDER, so every rank computes the same bits.
+// An aligned 8-byte store is single-copy atomic, so a word whose tag matches carries its value;
+// no memory fence is needed on either side and the latency is one NVLink hop.
+// Arenas are double buffered by epoch parity: a rank can only start pushing for epoch e+2 after
+// it consumed e+1, which needs every peer's e+1 data, which a peer sends only after it finished
+// consuming e. Epochs start at 1 and arenas at zero, so a stale word never matches.
 // No wait is unbounded: when the limit expires the kernel records a status word that the host
 // can read through mapped pinned memory, stops waiting and lets the launch drain.
 #pragma once
@@ -19,49 +21,65 @@
 
 typedef struct {
   int32_t world, rank;
-  float* slots[PSGD_MAX_WORLD];   // peer p's arena: [2][world][cap] floats
-  int32_t* flags[PSGD_MAX_WORLD]; // peer p's flag pad: [world] ints, flag[r] = last epoch published by r
+  uint2* slots[PSGD_MAX_WORLD];   // peer p's arena: [2][world][cap] words {value bits, epoch}
   int32_t* epoch;                 // local: last completed epoch of this channel
-  int32_t* arrive;                // local: [4] arrival counters (producer launch, consumer launch, spare)
+  int32_t* arrive;                // local: [4] arrival counters of consumer launches
   int32_t* status;                // mapped pinned host word: 0 ok, else PsgdStatus
-  int64_t cap;                    // floats per slot
+  int64_t cap;                    // words per slot
   uint64_t timeout_ns;
 } PsgdCommDev;
 
-__device__ __forceinline__ float* psgd_comm_slot(const PsgdCommDev& c, int peer, int epoch, int src_rank) {
+__device__ __forceinline__ uint2* psgd_comm_slot(const PsgdCommDev& c, int peer, int epoch, int src_rank) {
   return c.slots[peer] + ((int64_t)(epoch & 1) * c.world + src_rank) * c.cap;
 }
 
-// Called by ONE thread of the CTA that arrived last: publish `epoch` to every peer.
-__device__ __forceinline__ void psgd_comm_publish(const PsgdCommDev& c, int epoch) {
-  __threadfence_system();
-  for (int p = 0; p < c.world; ++p) psgd_st_release_sys(c.flags[p] + c.rank, epoch);
+__device__ __forceinline__ void psgd_comm_store(uint2* p, float v, int epoch) {
+  asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"((uint32_t)epoch) : "memory");
 }
 
-// Every thread of the CTA may call this; threads t < world poll one flag each. Returns false
-// when the wait was abandoned (limit hit now or by an earlier wait).
-__device__ __forceinline__ bool psgd_comm_wait_all(const PsgdCommDev& c, int epoch) {
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if ((int)threadIdx.x < c.world) {
-    const int* f = c.flags[c.rank] + threadIdx.x;
-    if (psgd_ld_acquire_sys(f) - epoch < 0) {
-      const uint64_t t0 = psgd_globaltimer_ns();
-      bool ok = true;
-      while (psgd_ld_acquire_sys(f) - epoch < 0) {
-        if (*((volatile int*)c.status) != 0) { ok = false; break; }
-        if (psgd_globaltimer_ns() - t0 > c.timeout_ns) {
-          *((volatile int*)c.status) = PSGD_TIMEOUT_PEER_BARRIER;
-          __threadfence_system();
-          ok = false;
-          break;
-        }
-        __nanosleep(64);
+__device__ __forceinline__ uint2 psgd_comm_peek(const uint2* p) {
+  uint2 w;
+  asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
+  return w;
+}
+
+// Value of a word of the own arena once its tag shows `epoch`. `ok` turns false (and stays false)
+// when the wait was abandoned: limit hit now, or already hit by an earlier wait of this launch.
+__device__ __forceinline__ float psgd_comm_load(const PsgdCommDev& c, const uint2* p, int epoch, bool& ok) {
+  uint2 w = psgd_comm_peek(p);
+  if ((int)w.y == epoch) return __uint_as_float(w.x);
+  if (!ok) return 0.f;
+  const uint64_t t0 = psgd_globaltimer_ns();
+  int spins = 0;
+  while (true) {
+    w = psgd_comm_peek(p);
+    if ((int)w.y == epoch) return __uint_as_float(w.x);
+    if ((++spins & 63) == 0) {
+      if (*((volatile int*)c.status) != 0) { ok = false; return 0.f; }
+      if (psgd_globaltimer_ns() - t0 > c.timeout_ns) {
+        *((volatile int*)c.status) = PSGD_TIMEOUT_PEER_BARRIER;
+        __threadfence_system();
+        ok = false;
+        return 0.f;
       }
-      if (!ok) s_ok = 0;
     }
   }
+}
+
+// Sum over ranks, in rank order, of element i of this epoch's slots of the own arena.
+__device__ __forceinline__ float psgd_comm_reduce(const PsgdCommDev& c, int epoch, int64_t i, bool& ok) {
+  float s = 0.f;
+  for (int r = 0; r < c.world; ++r) s += psgd_comm_load(c, psgd_comm_slot(c, c.rank, epoch, r) + i, epoch, ok);
+  return s;
+}
+
+// Consumer launches close the epoch: the CTA that arrives last advances the channel.
+__device__ __forceinline__ void psgd_comm_close_epoch(const PsgdCommDev& c, int epoch) {
   __syncthreads();
-  return s_ok != 0;
+  if (threadIdx.x == 0) {
+    if (psgd_atom_add_acqrel_gpu(c.arrive + 1, 1) == (int)gridDim.x - 1) {
+      c.arrive[1] = 0;
+      *c.epoch = epoch;
+    }
+  }
 }

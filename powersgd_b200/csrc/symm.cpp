@@ -59,10 +59,10 @@ PSGD_API int psgd_status_free(int* host_ptr) {
 
 PSGD_API int psgd_comm_desc_bytes() { return (int)sizeof(PsgdCommDev); }
 
-// Fills a host-side PsgdCommDev (the caller uploads it). slots / flags hold `world` pointers
-// each, indexed by rank (own allocation at index `rank`).
-PSGD_API int psgd_comm_fill(void* desc_out, int world, int rank, void* const* slots, void* const* flags,
-                            int* epoch, int* arrive, int* status_dev, long long cap, double timeout_ms) {
+// Fills a host-side PsgdCommDev (the caller uploads it). `slots` holds `world` arena pointers
+// indexed by rank (own allocation at index `rank`); an arena has 2 * world * cap 8-byte words.
+PSGD_API int psgd_comm_fill(void* desc_out, int world, int rank, void* const* slots, int* epoch, int* arrive,
+                            int* status_dev, long long cap, double timeout_ms) {
   if (world < 1 || world > PSGD_MAX_WORLD || rank < 0 || rank >= world) {
     psgd_set_error("psgd_comm_fill: world %d / rank %d out of range (max %d ranks)", world, rank, PSGD_MAX_WORLD);
     return -1;
@@ -72,8 +72,7 @@ PSGD_API int psgd_comm_fill(void* desc_out, int world, int rank, void* const* sl
   d.world = world;
   d.rank = rank;
   for (int p = 0; p < world; ++p) {
-    d.slots[p] = (float*)slots[p];
-    d.flags[p] = (int32_t*)flags[p];
+    d.slots[p] = (uint2*)slots[p];
   }
   d.epoch = epoch;
   d.arrive = arrive;

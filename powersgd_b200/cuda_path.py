@@ -532,7 +532,7 @@ class NativeFlatAllReduce:
             workers > 1
             and self.comm is None
             and os.environ.get("PSGD_B200_COMM", "p2p") == "p2p"
-            and 2 * workers * total * 4 <= self.P2P_ARENA_LIMIT_BYTES
+            and 2 * workers * total * 8 <= self.P2P_ARENA_LIMIT_BYTES
         ):
             from .parallel.symm import Channel
 

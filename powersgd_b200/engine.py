@@ -37,6 +37,7 @@ class TrainStep:
         cuda_graph: bool = True,
         eager_steps: int = 3,
         channels_last: bool = True,
+        grad_clip: Optional[float] = None,
     ):
         self.model = model
         self.loss_fn = loss_fn
@@ -48,6 +49,8 @@ class TrainStep:
         # 4-D inputs are fed in NHWC: cuDNN's tensor-core convolutions run ~1.7x faster on
         # B200 that way, while parameters and their gradients stay contiguous [out, in*kh*kw].
         self.channels_last = bool(channels_last) and self.device.type == "cuda"
+        # optional global gradient-norm clipping before aggregation (the LSTM task clips at 0.4)
+        self.grad_clip = grad_clip
         self._steps_done = 0
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._static_x: Optional[torch.Tensor] = None
@@ -63,9 +66,18 @@ class TrainStep:
             return x.contiguous(memory_format=torch.channels_last)
         return x
 
+    def _clip(self) -> None:
+        if self.grad_clip is not None:
+            # foreach implementation: no host synchronisation, capturable
+            torch.nn.utils.clip_grad_norm_(self._params(), self.grad_clip, foreach=True)
+
+    def _params(self):
+        return [p for g in self.optimizer.param_groups for p in g["params"]]
+
     def _eager(self, x: torch.Tensor, y: torch.Tensor, time_aggregate: bool = False) -> torch.Tensor:
         loss = self.loss_fn(self.model(self._format(x)), y)
         loss.backward()
+        self._clip()
         if time_aggregate and self.device.type == "cuda":
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
@@ -118,6 +130,7 @@ class TrainStep:
         with torch.cuda.graph(graph, pool=self._pool):
             loss = self.loss_fn(self.model(self._static_x), self._static_y)
             loss.backward()
+            self._clip()
             agg.fused_step(self.optimizer, prepared=True)
             if self._static_loss is None:
                 self._static_loss = loss.detach()

@@ -1,8 +1,8 @@
 """Symmetric memory and in-kernel collective channels over NVLink peer mappings.
 
 `Channel` is the host-side handle of one stream of collectives (csrc/psgd_comm.cuh): it
-allocates this rank's slot arena and flag pad, exchanges CUDA-IPC handles with the other
-ranks once (through the existing torch.distributed group — the only use of a library
+allocates this rank's slot arena (8-byte {value, epoch} words), exchanges CUDA-IPC handles with
+the other ranks once (through the existing torch.distributed group — the only use of a library
 collective), maps every peer's arena, and uploads the device descriptor that kernels take.
 
 Failure handling: device-side waits are bounded (`timeout_ms`, default from
@@ -98,8 +98,7 @@ class Channel:
         self.timeout_ms = default_timeout_ms() if timeout_ms is None else float(timeout_ms)
         device = torch.device("cuda", torch.cuda.current_device())
         self.device = device
-        self.slots = SymmetricBuffer(2 * self.world * self.cap * 4, group)
-        self.flags = SymmetricBuffer(256, group)
+        self.slots = SymmetricBuffer(2 * self.world * self.cap * 8, group)
         # local bookkeeping words: epoch, arrival counters
         self._words = torch.zeros(16, dtype=torch.int32, device=device)
         host_ptr, dev_ptr = ctypes.POINTER(ctypes.c_int)(), ctypes.POINTER(ctypes.c_int)()
@@ -109,11 +108,10 @@ class Channel:
         nbytes = self.lib.psgd_comm_desc_bytes()
         host_desc = (ctypes.c_ubyte * nbytes)()
         slots = (ctypes.c_void_p * self.world)(*self.slots.ptrs)
-        flags = (ctypes.c_void_p * self.world)(*self.flags.ptrs)
         base = self._words.data_ptr()
         native.check(
             self.lib.psgd_comm_fill(
-                host_desc, self.world, self.rank, slots, flags, _vp(base), _vp(base + 16), _vp(self._status_dev),
+                host_desc, self.world, self.rank, slots, _vp(base), _vp(base + 16), _vp(self._status_dev),
                 ctypes.c_longlong(self.cap), ctypes.c_double(self.timeout_ms),
             ),
             "psgd_comm_fill",
@@ -139,7 +137,7 @@ class Channel:
     def reset_status(self) -> None:
         self._status_host[0] = 0
 
-    def all_reduce_(self, tensor: torch.Tensor, scale: float = 1.0, max_blocks: int = 128) -> torch.Tensor:
+    def all_reduce_(self, tensor: torch.Tensor, scale: float = 1.0, max_blocks: int = 296) -> torch.Tensor:
         """In-place one-launch SUM all-reduce (times `scale`) of a contiguous float32 tensor."""
         if tensor.numel() > self.cap:
             raise ValueError(f"message of {tensor.numel()} floats exceeds the channel capacity {self.cap}")
@@ -155,7 +153,6 @@ class Channel:
 
     def close(self) -> None:
         self.slots.close()
-        self.flags.close()
         if self._status_host:
             self.lib.psgd_status_free(self._status_host)
             self._status_host = None
