@@ -642,6 +642,9 @@ class FusedSGDDriver:
     def prepare(self, optimizer) -> None:
         """Host side of a step: momentum buffers, hyper-parameter table, async upload."""
         fresh = self._collect(optimizer)
+        # the residual tensors may have been replaced (e.g. after loading a checkpoint)
+        if any(p.grad.data_ptr() != g.data_ptr() for p, g in zip(self._params[:4], self._grads[:4])):
+            self._grads = [p.grad.data for p in self._params]
         groups = optimizer.param_groups
         table = np.zeros(len(groups), dtype=layout.HYPER_DTYPE)
         for gi, group in enumerate(groups):
@@ -659,6 +662,10 @@ class FusedSGDDriver:
             self._slots = [torch.empty(nbytes, dtype=torch.uint8).pin_memory() for _ in range(self.RING)]
             self._slot_events = [None] * self.RING
             self._hyper_dev = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        blob = table.tobytes()
+        if not fresh and blob == getattr(self, "_last_blob", None):
+            return  # nothing changed since the last upload: the device table is already right
+        self._last_blob = blob
         i = self._cursor
         self._cursor = (i + 1) % self.RING
         if self._slot_events[i] is not None:
@@ -668,9 +675,6 @@ class FusedSGDDriver:
         ev = torch.cuda.Event()
         ev.record()
         self._slot_events[i] = ev
-        # the residual tensors may have been replaced (e.g. after loading a checkpoint)
-        if any(p.grad.data_ptr() != g.data_ptr() for p, g in zip(self._params[:4], self._grads[:4])):
-            self._grads = [p.grad.data for p in self._params]
 
     def step(self, optimizer, prepared: bool = False) -> None:
         if not prepared:
