@@ -230,6 +230,7 @@ def main():
         return float(t.item())
 
     # ---- warm-up (also builds descriptors / captures the graph) -----------------------------
+    # at least 3 untimed steps: two run eagerly (cuDNN autotuning, lazy buffers), the third records the graph
     for i in range(max(args.warmup, 3)):
         loss = step(xs_dev[i % n_slots], ys_dev[i % n_slots])
     barrier()

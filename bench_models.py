@@ -162,6 +162,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    # at least 3 untimed steps: two run eagerly (cuDNN autotuning, lazy buffers), the third records the graph
     for i in range(max(args.warmup, 3)):
         step(xs_dev[i % 8], ys_dev[i % 8])
     barrier()

@@ -35,7 +35,7 @@ class TrainStep:
         optimizer: torch.optim.Optimizer,
         aggregator,
         cuda_graph: bool = True,
-        eager_steps: int = 3,
+        eager_steps: int = 2,
         channels_last: bool = True,
         grad_clip: Optional[float] = None,
     ):
