@@ -52,14 +52,19 @@ class ClockSampler:
         "clocks_event_reasons.sw_power_cap"
     )
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, enabled: bool = True):
         self.index = index
         self.proc = None
+        # one sampler per job (rank 0): every nvidia-smi query takes driver locks, and one poller
+        # per rank visibly perturbs an 8-GPU run
+        self.enabled = enabled
 
     def start(self):
+        if not self.enabled:
+            return
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
                 stdout=subprocess.PIPE,
                 stderr=subprocess.DEVNULL,
                 text=True,
@@ -68,6 +73,8 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        if not self.enabled:
+            return None
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -236,7 +243,7 @@ def main():
     barrier()
 
     # ---- device-timed region: inputs resident, no host read-back ----------------------------
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(local, enabled=rank == 0)
     sampler.start()
     time.sleep(0.3)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -295,6 +302,7 @@ def main():
                 "optimizer": {"sgd_lr": LR, "momentum": MOMENTUM, "nesterov": True, "weight_decay": WD},
                 "l2": "per-step working set (activations + gradients, > 1 GB at batch 128) exceeds the 126 MB L2; no explicit flush",
                 "cuda_graph": bool(args.impl == "ours" and not args.no_graph),
+                "host_cpus": os.cpu_count(),
             },
             "clocks": clocks,
             "e2e": {

@@ -166,7 +166,7 @@ def main():
     for i in range(max(args.warmup, 3)):
         step(xs_dev[i % 8], ys_dev[i % 8])
     barrier()
-    sampler = headline.ClockSampler(local)
+    sampler = headline.ClockSampler(local, enabled=rank == 0)
     sampler.start()
     time.sleep(0.3)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

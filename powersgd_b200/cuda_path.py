@@ -85,6 +85,7 @@ class TilePlan:
         self.nn_rows = lib.psgd_gemm_nn_tile_rows(self.max_r)
         self.nn_cols_cap = 1024
         self.rp_tc = lib.psgd_gemm_tc_rank_pad(self.max_r)
+        self.fin_tc_ok = False  # set by the compressor: (half-iterations x rank) fits the tensor-core finalize
 
     def vec_ok(self, mi: int) -> bool:
         g = self.plan.groups[self.mats[mi][0]]
@@ -95,7 +96,7 @@ class TilePlan:
         matrices flagged in `tc_flags`, tensor-core tiles (key "tc")."""
         nt = {4: [], 1: [], "tc": []}
         nn = {4: [], 1: [], "tc": []}
-        fin = {4: [], 1: []}
+        fin = {4: [], 1: [], "tc": []}
         ticket = 0
         nt_slots = nn_slots = tc_slots = 0
         tc_flags = tc_flags or [False] * len(self.mats)
@@ -106,9 +107,14 @@ class TilePlan:
         for mi, (gi, _pos, _idx) in enumerate(self.mats):
             g = self.plan.groups[gi]
             v = 4 if vec_flags[mi] else 1
-            for r0 in range(0, g.n, 32):
-                for c0 in range(0, g.m, 128):
-                    fin[v].append((mi, r0, min(32, g.n - r0), c0, min(128, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
+            if tc_flags[mi] and self.fin_tc_ok:
+                for r0 in range(0, g.n, 128):
+                    for c0 in range(0, g.m, 64):
+                        fin["tc"].append((mi, r0, min(128, g.n - r0), c0, min(64, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
+            else:
+                for r0 in range(0, g.n, 32):
+                    for c0 in range(0, g.m, 128):
+                        fin[v].append((mi, r0, min(32, g.n - r0), c0, min(128, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
             if tc_flags[mi]:
                 row_blocks = _split_even(g.n, tc_k, 32)
                 for c0 in range(0, g.m, 128):
@@ -175,6 +181,10 @@ class NativeCompressor:
         self.plan = core.plan
         self.tiles = TilePlan(core.plan, self.lib)
         self.T = core.config.num_iters_per_step
+        self.tiles.fin_tc_ok = (
+            self.T * self.tiles.max_r <= self.lib.psgd_finalize_tc_max_k()
+            and os.environ.get("PSGD_B200_FINALIZE", "auto") != "ffma"
+        )
         if self.T > layout.MAX_HIST:
             raise ValueError(f"num_iters_per_step {self.T} exceeds the compiled maximum {layout.MAX_HIST}")
         nm = len(self.tiles.mats)
@@ -366,6 +376,27 @@ class NativeCompressor:
             else:
                 rloc.append(self.h_in[t]); rsum.append(self.h_in[t])
                 lloc.append(self.h_loc[t]); lsum.append(self.h_sum[t])
+        tiles, count = self._tiles_dev["fin"]["tc"]
+        if count:
+            code = self.lib.psgd_finalize_tc_launch(
+                _ptr(self._mats_dev),
+                _ptr(tiles),
+                count,
+                _ptr(self._maps_dev),
+                _ptr(self._hyper_dev),
+                len(sides),
+                self.tiles.max_r,
+                ctypes.cast(_ptr_array(lloc), ctypes.c_void_p),
+                ctypes.cast(_ptr_array(rloc), ctypes.c_void_p),
+                ctypes.cast(_ptr_array(lsum), ctypes.c_void_p),
+                ctypes.cast(_ptr_array(rsum), ctypes.c_void_p),
+                1.0 / workers,
+                1 if fused_sgd else 0,
+                _ptr(self._tc_status),
+                _stream_ptr(),
+            )
+            native.check(code, "psgd_finalize_tc_launch")
+            self.launches += 1
         for v in (4, 1):
             tiles, count = self._tiles_dev["fin"][v]
             if count == 0:

@@ -48,6 +48,8 @@ _OPTIONAL = {
     "psgd_gemm_tc_rank_pad": (i32, [i32]),
     "psgd_tma_encode_matrix": (i32, [vp, vp, i32, i32]),
     "psgd_gemm_tc_launch": (i32, [i32, i32, i32, vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, vp, vp]),
+    "psgd_finalize_tc_max_k": (i32, []),
+    "psgd_finalize_tc_launch": (i32, [vp, vp, i32, vp, vp, i32, i32, vp, vp, vp, vp, f32, i32, vp, vp]),
     "psgd_symm_alloc": (i32, [C.c_size_t, C.POINTER(vp)]),
     "psgd_symm_free": (i32, [vp]),
     "psgd_symm_handle_bytes": (i32, []),
