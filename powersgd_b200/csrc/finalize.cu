@@ -66,6 +66,19 @@ __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs
 #pragma unroll
     for (int c = 0; c < 4; ++c) accE[u][c] = accA[u][c] = 0.f;
 
+  // Single-worker variant: there is register room to issue the loads of the gradient tile before
+  // the rank-K update is computed, so their latency overlaps the panel staging and the FMA loop.
+  float4 gpre[4];
+  if (VEC == 4 && SAME) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int lr = warp * 4 + u;
+      gpre[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (lr < t.rows && lane * 4 < t.cols)
+        gpre[u] = *reinterpret_cast<const float4*>(mt.grad + (long long)(t.row0 + lr) * m + t.col0 + lane * 4);
+    }
+  }
+
   for (int k0 = 0; k0 < K; k0 += FIN_KC) {
     const int kc = min(FIN_KC, K - k0);
     __syncthreads();
@@ -130,7 +143,7 @@ __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs
     if (VEC == 4) {
       const int col = t.col0 + lane * 4;
       if (lane * 4 >= t.cols) continue;
-      const float4 g = *reinterpret_cast<const float4*>(mt.grad + rowoff + col);
+      const float4 g = SAME ? gpre[u] : *reinterpret_cast<const float4*>(mt.grad + rowoff + col);
       float gv[4] = {g.x, g.y, g.z, g.w};
       float av[4];
 #pragma unroll

@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_kernel(OrthArgs a) {
 #pragma unroll
     for (int k = 0; k < RT; ++k) acc[k] = 0.0;
     if (j < r) {
+#pragma unroll 4
       for (long long row = rl; row < len; row += NRL) {
         const float* xr = x + row * r;
         const double xj = (double)xr[j];
@@ -192,6 +193,7 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_kernel(OrthArgs a) {
     __syncthreads();
 
     // ---- X <- X' R^-1 --------------------------------------------------------------------
+#pragma unroll 2
     for (long long row = tid; row < len; row += ORTH_THREADS) {
       float* xr = x + row * r;
       double xin[RT];
@@ -229,6 +231,7 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_kernel(OrthArgs a) {
         for (int k = 0; k < RT; ++k) acc[k] = 0.0;
         if (j < r) {
           const long long lo = (long long)s * u.sub_len, hi = lo + u.sub_len;
+#pragma unroll 4
           for (long long row = lo + rl; row < hi; row += NRL) {
             const double fj = (double)f[row * r + j];
             const float* xr = x + row * r;

@@ -183,7 +183,7 @@ class NativeCompressor:
         self.T = core.config.num_iters_per_step
         self.tiles.fin_tc_ok = (
             self.T * self.tiles.max_r <= self.lib.psgd_finalize_tc_max_k()
-            and os.environ.get("PSGD_B200_FINALIZE", "auto") != "ffma"
+            and os.environ.get("PSGD_B200_FINALIZE", "ffma") == "tc"
         )
         if self.T > layout.MAX_HIST:
             raise ValueError(f"num_iters_per_step {self.T} exceeds the compiled maximum {layout.MAX_HIST}")
