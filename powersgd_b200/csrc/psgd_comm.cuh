@@ -24,7 +24,9 @@ typedef struct {
   uint2* slots[PSGD_MAX_WORLD];   // peer p's arena: [2][world][cap] words {value bits, epoch}
   int32_t* epoch;                 // local: last completed epoch of this channel
   int32_t* arrive;                // local: [4] arrival counters of consumer launches
-  int32_t* status;                // mapped pinned host word: 0 ok, else PsgdStatus
+  int32_t* abort_flag;            // local device word: non-zero once a wait on this channel ran out
+  int32_t* status;                // mapped pinned host word: 0 ok, else PsgdStatus (written once, on a
+                                  // timeout; never read by kernels - a read is a PCIe round trip)
   int64_t cap;                    // words per slot
   uint64_t timeout_ns;
 } PsgdCommDev;
@@ -54,9 +56,11 @@ __device__ __forceinline__ float psgd_comm_load(const PsgdCommDev& c, const uint
   while (true) {
     w = psgd_comm_peek(p);
     if ((int)w.y == epoch) return __uint_as_float(w.x);
-    if ((++spins & 63) == 0) {
-      if (*((volatile int*)c.status) != 0) { ok = false; return 0.f; }
+    if ((++spins & 15) == 0) __nanosleep(32);   // keep thousands of pollers from saturating L2
+    if ((spins & 255) == 0) {
+      if (*((volatile int*)c.abort_flag) != 0) { ok = false; return 0.f; }
       if (psgd_globaltimer_ns() - t0 > c.timeout_ns) {
+        *((volatile int*)c.abort_flag) = 1;
         *((volatile int*)c.status) = PSGD_TIMEOUT_PEER_BARRIER;
         __threadfence_system();
         ok = false;

@@ -61,8 +61,8 @@ PSGD_API int psgd_comm_desc_bytes() { return (int)sizeof(PsgdCommDev); }
 
 // Fills a host-side PsgdCommDev (the caller uploads it). `slots` holds `world` arena pointers
 // indexed by rank (own allocation at index `rank`); an arena has 2 * world * cap 8-byte words.
-PSGD_API int psgd_comm_fill(void* desc_out, int world, int rank, void* const* slots, int* epoch, int* arrive,
-                            int* status_dev, long long cap, double timeout_ms) {
+PSGD_API int psgd_comm_fill(void* desc_out, int world, int rank, void* const* slots, int* words, int* status_dev,
+                            long long cap, double timeout_ms) {
   if (world < 1 || world > PSGD_MAX_WORLD || rank < 0 || rank >= world) {
     psgd_set_error("psgd_comm_fill: world %d / rank %d out of range (max %d ranks)", world, rank, PSGD_MAX_WORLD);
     return -1;
@@ -74,8 +74,9 @@ PSGD_API int psgd_comm_fill(void* desc_out, int world, int rank, void* const* sl
   for (int p = 0; p < world; ++p) {
     d.slots[p] = (uint2*)slots[p];
   }
-  d.epoch = epoch;
-  d.arrive = arrive;
+  d.epoch = words;           // 16 zeroed device ints: [0] epoch, [4..7] arrival counters, [8] abort flag
+  d.arrive = words + 4;
+  d.abort_flag = words + 8;
   d.status = status_dev;
   d.cap = cap;
   d.timeout_ns = (uint64_t)(timeout_ms * 1e6);

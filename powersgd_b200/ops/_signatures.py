@@ -59,7 +59,7 @@ _OPTIONAL = {
     "psgd_status_alloc": (i32, [C.POINTER(C.POINTER(i32)), C.POINTER(C.POINTER(i32))]),
     "psgd_status_free": (i32, [C.POINTER(i32)]),
     "psgd_comm_desc_bytes": (i32, []),
-    "psgd_comm_fill": (i32, [vp, i32, i32, vp, vp, vp, vp, i64, C.c_double]),
+    "psgd_comm_fill": (i32, [vp, i32, i32, vp, vp, vp, i64, C.c_double]),
     "psgd_factor_reduce_launch": (i32, [vp, i64, vp, vp, vp]),
     "psgd_allreduce_oneshot_launch": (i32, [vp, vp, vp, i64, f32, i32, vp]),
 }

@@ -111,7 +111,7 @@ class Channel:
         base = self._words.data_ptr()
         native.check(
             self.lib.psgd_comm_fill(
-                host_desc, self.world, self.rank, slots, _vp(base), _vp(base + 16), _vp(self._status_dev),
+                host_desc, self.world, self.rank, slots, _vp(base), _vp(self._status_dev),
                 ctypes.c_longlong(self.cap), ctypes.c_double(self.timeout_ms),
             ),
             "psgd_comm_fill",
@@ -136,6 +136,7 @@ class Channel:
 
     def reset_status(self) -> None:
         self._status_host[0] = 0
+        self._words[8] = 0
 
     def all_reduce_(self, tensor: torch.Tensor, scale: float = 1.0, max_blocks: int = 296) -> torch.Tensor:
         """In-place one-launch SUM all-reduce (times `scale`) of a contiguous float32 tensor."""
