@@ -81,7 +81,8 @@ class AllReduce(Aggregator):
         if len(gradients) == 0:
             return []
         device = gradients[0].device
-        if _pick_backend(self._backend_request, device) == "native" and gradients[0].dtype == torch.float32:
+        plain = all(g.dtype == torch.float32 and g.is_contiguous() for g in gradients)
+        if _pick_backend(self._backend_request, device) == "native" and plain:
             from .cuda_path import NativeFlatAllReduce
 
             if self._native is None:
@@ -263,7 +264,8 @@ class BasicPowerSGD(Aggregator):
         if len(gradients) == 0:
             self.step_counter += 1
             return []
-        if self.backend == "native" and self.dtype == torch.float32:
+        native_ok = self.dtype == torch.float32 and all(g.is_contiguous() and g.dtype == torch.float32 for g in gradients)
+        if self.backend == "native" and native_ok:
             from .cuda_path import NativeCompressor
 
             if self._native is None:

@@ -129,11 +129,18 @@ def scenario_powersgd_native():
             x.add_(z)
             y.add_(z)
     comm = ours._powersgd._native.comm
-    assert comm is not None, "expected the in-kernel all-reduce path"
-    comm.check()
+    if os.environ.get("PSGD_B200_COMM", "p2p") == "p2p":
+        assert comm is not None, "expected the in-kernel all-reduce path"
+        comm.check()
+    else:
+        assert comm is None
     dist.barrier()
     if rank == 0:
         print("SCENARIO-OK")
+
+
+def scenario_powersgd_native_nccl():
+    scenario_powersgd_native()
 
 
 def scenario_train_step_graph():

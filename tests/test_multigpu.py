@@ -16,3 +16,17 @@ ENV = {"NCCL_NVLS_ENABLE": "0"}
 def test_two_gpu_scenarios(name):
     res = run_scenario(name, nproc=2, timeout=600, env=ENV)
     assert "SCENARIO-OK" in res.stdout, res.stdout[-3000:] + res.stderr[-6000:]
+
+
+@needs_two
+def test_two_gpu_tensor_core_path_with_peer_push():
+    """The tcgen05 product kernels push their epilogue to the peers too."""
+    res = run_scenario("powersgd_native", nproc=2, timeout=600, env=dict(ENV, PSGD_B200_GEMM="tc"))
+    assert "SCENARIO-OK" in res.stdout, res.stdout[-3000:] + res.stderr[-6000:]
+
+
+@needs_two
+def test_two_gpu_library_allreduce_path():
+    """PSGD_B200_COMM=nccl: same kernels, factors and flat buffer reduced by the library (eager)."""
+    res = run_scenario("powersgd_native_nccl", nproc=2, timeout=600, env=dict(ENV, PSGD_B200_COMM="nccl"))
+    assert "SCENARIO-OK" in res.stdout, res.stdout[-3000:] + res.stderr[-6000:]
