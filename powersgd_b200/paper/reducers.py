@@ -31,6 +31,7 @@ import torch.distributed as dist
 
 from ..orthogonalization import gram_schmidt_
 from ..ops import signpack
+from ..ops.topk import topk_abs
 from ..utils import TensorBuffer, n_bits
 from ..utils.timer import Timer
 
@@ -387,15 +388,12 @@ class TopKReducer(Reducer):
             values = torch.empty(ends[-1], device=self.device)
             positions = torch.empty(ends[-1], device=self.device, dtype=torch.int32)
         with self.timer("reduce.topk", verbosity=2):
-            for t, lo, hi, k in zip(grad_in, starts, ends, sizes):
-                flat = t.reshape(-1)
-                _, idx = torch.topk(flat.abs(), k, sorted=False)
-                values[lo:hi] = flat[idx]
+            # selection, gather and the error-feedback write (memory = x with the taken entries
+            # zeroed) are one fused operation
+            for t, mem, lo, hi, k in zip(grad_in, memory_out, starts, ends, sizes):
+                vals, idx = topk_abs(t, k, memory=mem)
+                values[lo:hi] = vals
                 positions[lo:hi] = idx
-        with self.timer("reduce.memory", verbosity=2):
-            for t, mem, lo, hi in zip(grad_in, memory_out, starts, ends):
-                mem.copy_(t)
-                mem.view(-1)[positions[lo:hi].long()] = 0.0
         with self.timer("reduce.gather", verbosity=2):
             all_values = _gather_all(values, self.n_workers)
             all_positions = _gather_all(positions, self.n_workers)
@@ -422,11 +420,10 @@ class GlobalTopKReducer(Reducer):
             flat = packed.buffer
             k = _top_size(self.compression, flat.nelement())
         with self.timer("reduce.topk", verbosity=2):
-            _, positions = torch.topk(flat.abs(), k, sorted=False)
-            values = flat[positions].contiguous()
+            residual = torch.empty_like(flat)
+            values, positions = topk_abs(flat, k, memory=residual)
+            positions = positions.long()
         with self.timer("reduce.set_memory", verbosity=2):
-            residual = flat.clone()
-            residual[positions] = 0.0
             packed.buffer = residual
             packed.unpack(memory_out)
         with self.timer("reduce.reduce", verbosity=2):
