@@ -175,6 +175,16 @@ class PowerSGD(Aggregator):
                     return False
         return True
 
+    def begin_step(self) -> None:
+        """Optional hint, called before forward: lets the native back end start the work of the
+        coming aggregation that does not depend on the gradients (the first orthonormalisation)
+        on a side stream, overlapped with forward and backward. A no-op otherwise."""
+        if self.step_counter < self.config.start_compressing_after_num_steps:
+            return
+        native = self._powersgd._native
+        if native is not None and native._key is not None:
+            native.begin_step()
+
     def fused_step(self, optimizer: torch.optim.Optimizer, prepared: bool = False) -> None:
         """Aggregate and apply SGD inside the native kernels: the averaged gradient is never
         written to memory. Numerically the same update as `optimizer_step` with

@@ -200,6 +200,8 @@ class NativeCompressor:
         self._out_arena: Optional[torch.Tensor] = None
         self._hyper_dev = _to_device(self._default_hyper(), self.device)
         self.launches = 0  # kernels launched by the last aggregate()
+        self._side_stream = torch.cuda.Stream(device=self.device)
+        self._early = None  # (side, event) of an orthonormalisation issued by begin_step()
         # multi-GPU: factors are all-reduced by the product kernels themselves (peer pushes) plus
         # a small consumer kernel; PSGD_B200_COMM=nccl selects the library all-reduce instead
         self.comm = None
@@ -436,7 +438,15 @@ class NativeCompressor:
                 out_side_i = self.h_loc[i] if sides[i] == left else self.h_in[i]
                 same.append(in_side_i)
                 other.append(out_side_i)
-            self._orth(side, state_in, self.h_in[t], same, self.cmat[t])
+            if t == 0 and self._early is not None:
+                # the first basis was orthonormalised on the side stream while forward / backward ran
+                early_side, event = self._early
+                self._early = None
+                torch.cuda.current_stream().wait_event(event)
+                if early_side != side:  # state changed under us (e.g. a checkpoint was loaded): redo
+                    self._orth(side, state_in, self.h_in[t], same, self.cmat[t])
+            else:
+                self._orth(side, state_in, self.h_in[t], same, self.cmat[t])
             self._gemm(left, self.h_in[t], self.h_loc[t], other, self.cmat[t])
             total = state_out.numel()
             if workers > 1 and self.comm is not None:
@@ -455,6 +465,29 @@ class NativeCompressor:
 
     def _allreduce_sum(self, flat: torch.Tensor) -> None:
         dist.all_reduce(flat)
+
+    def begin_step(self) -> None:
+        """Orthonormalise the basis of the first half-iteration NOW, on a side stream.
+
+        That basis only depends on the factors left by the previous step, not on the gradients
+        about to be computed, so the launch overlaps with forward / backward; `aggregate` then
+        waits on an event instead of launching it. Captured in a CUDA graph this is a parallel
+        branch of the step."""
+        if self._early is not None:
+            return
+        core = self.core
+        left = (core.step_counter * self.T) % 2 == 0
+        side = "p" if left else "q"
+        state_in = core._ps_buffer if left else core._qs_buffer
+        main = torch.cuda.current_stream()
+        fork = torch.cuda.Event()
+        fork.record(main)
+        self._side_stream.wait_event(fork)
+        with torch.cuda.stream(self._side_stream):
+            self._orth(side, state_in, self.h_in[0], [], self.cmat[0])
+            done = torch.cuda.Event()
+            done.record(self._side_stream)
+        self._early = (side, done)
 
     # -- public ----------------------------------------------------------------------------
     def aggregate(self, gradients: List[torch.Tensor]) -> List[torch.Tensor]:
@@ -641,6 +674,7 @@ class FusedSGDDriver:
         self._flat_all = NativeFlatAllReduce()
         self._flat_plain = NativeFlatAllReduce()
         self.launches = 0
+        self._side: Optional[torch.cuda.Stream] = None
 
     def _collect(self, optimizer):
         groups = optimizer.param_groups
@@ -723,6 +757,28 @@ class FusedSGDDriver:
         pick = lambda xs, keep: [x for x, k in zip(xs, mask) if k == keep]  # noqa: E731
         core = agg._powersgd
         self.launches = 0
+        plain = pick(grads, False)
+        joined = None
+        if plain and core.params:
+            # the flat all-reduce + SGD of the uncompressed tensors is independent of the low-rank
+            # path (own channel, own tensors): run it as a parallel branch on a side stream
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.device)
+            fork = torch.cuda.Event()
+            fork.record(torch.cuda.current_stream())
+            self._side.wait_event(fork)
+            with torch.cuda.stream(self._side):
+                self._flat_plain.aggregate_and_step(
+                    plain, pick(params, False), pick(moms, False), pick(index, False), hyper_dev
+                )
+                joined = torch.cuda.Event()
+                joined.record(self._side)
+            self.launches += self._flat_plain.launches
+        elif plain:
+            self._flat_plain.aggregate_and_step(
+                plain, pick(params, False), pick(moms, False), pick(index, False), hyper_dev
+            )
+            self.launches += self._flat_plain.launches
         if core.params:
             if core._native is None:
                 core._native = NativeCompressor(core)
@@ -731,9 +787,5 @@ class FusedSGDDriver:
             )
             core.step_counter += 1
             self.launches += core._native.launches
-        plain = pick(grads, False)
-        if plain:
-            self._flat_plain.aggregate_and_step(
-                plain, pick(params, False), pick(moms, False), pick(index, False), hyper_dev
-            )
-            self.launches += self._flat_plain.launches
+        if joined is not None:
+            torch.cuda.current_stream().wait_event(joined)

@@ -74,7 +74,13 @@ class TrainStep:
     def _params(self):
         return [p for g in self.optimizer.param_groups for p in g["params"]]
 
+    def _begin(self) -> None:
+        begin = getattr(self.aggregator, "begin_step", None)
+        if begin is not None:
+            begin()
+
     def _eager(self, x: torch.Tensor, y: torch.Tensor, time_aggregate: bool = False) -> torch.Tensor:
+        self._begin()
         loss = self.loss_fn(self.model(self._format(x)), y)
         loss.backward()
         self._clip()
@@ -128,6 +134,7 @@ class TrainStep:
         graph = torch.cuda.CUDAGraph()
         torch.cuda.synchronize()
         with torch.cuda.graph(graph, pool=self._pool):
+            self._begin()
             loss = self.loss_fn(self.model(self._static_x), self._static_y)
             loss.backward()
             self._clip()

@@ -174,3 +174,40 @@ def test_determinism_same_inputs_same_bits():
     for a, b in zip(outs[0], outs[1]):
         for x, y in zip(a, b):
             assert torch.equal(x, y)
+
+
+def test_train_step_graph_matches_plain_loop():
+    """TrainStep (side-stream branches, CUDA-graph replay) follows the same trajectory as the
+    documented plain loop (backward + optimizer_step)."""
+    from powersgd_b200.engine import TrainStep
+
+    dev = torch.device("cuda:0")
+
+    def make():
+        torch.manual_seed(4)
+        model = torch.nn.Sequential(torch.nn.Linear(96, 160), torch.nn.Tanh(), torch.nn.Linear(160, 64), torch.nn.Tanh(),
+                                    torch.nn.Linear(64, 10)).to(dev)
+        params = list(model.parameters())
+        opt = torch.optim.SGD(params, lr=0.05, momentum=0.9, nesterov=True, weight_decay=1e-4)
+        agg = PowerSGD(params, Config(rank=2, min_compression_rate=2, num_iters_per_step=2, start_compressing_after_num_steps=1))
+        return model, opt, agg
+
+    g = torch.Generator().manual_seed(0)
+    batches = [(torch.randn(32, 96, generator=g).to(dev), torch.randint(0, 10, (32,), generator=g).to(dev)) for _ in range(8)]
+    ma, oa, pa = make()
+    step = TrainStep(ma, torch.nn.functional.cross_entropy, oa, pa, cuda_graph=True)
+    la = [float(step(x, y).item()) for x, y in batches]
+    assert step._graphs, "never captured"
+    mb, ob, pb = make()
+    lb = []
+    for x, y in batches:
+        loss = torch.nn.functional.cross_entropy(mb(x), y)
+        loss.backward()
+        optimizer_step(ob, pb)
+        lb.append(float(loss.item()))
+    assert pa.step_counter == pb.step_counter == 8
+    assert pa._powersgd.step_counter == pb._powersgd.step_counter == 7
+    for a, b in zip(la, lb):
+        assert abs(a - b) < 1e-4 * max(1.0, abs(b)), (la, lb)
+    for p, q in zip(ma.parameters(), mb.parameters()):
+        assert _rel(p.detach(), q.detach()) < 1e-4
