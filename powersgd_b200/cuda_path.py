@@ -674,7 +674,6 @@ class FusedSGDDriver:
         self._flat_all = NativeFlatAllReduce()
         self._flat_plain = NativeFlatAllReduce()
         self.launches = 0
-        self._side: Optional[torch.cuda.Stream] = None
 
     def _collect(self, optimizer):
         groups = optimizer.param_groups
@@ -757,28 +756,6 @@ class FusedSGDDriver:
         pick = lambda xs, keep: [x for x, k in zip(xs, mask) if k == keep]  # noqa: E731
         core = agg._powersgd
         self.launches = 0
-        plain = pick(grads, False)
-        joined = None
-        if plain and core.params:
-            # the flat all-reduce + SGD of the uncompressed tensors is independent of the low-rank
-            # path (own channel, own tensors): run it as a parallel branch on a side stream
-            if self._side is None:
-                self._side = torch.cuda.Stream(device=self.device)
-            fork = torch.cuda.Event()
-            fork.record(torch.cuda.current_stream())
-            self._side.wait_event(fork)
-            with torch.cuda.stream(self._side):
-                self._flat_plain.aggregate_and_step(
-                    plain, pick(params, False), pick(moms, False), pick(index, False), hyper_dev
-                )
-                joined = torch.cuda.Event()
-                joined.record(self._side)
-            self.launches += self._flat_plain.launches
-        elif plain:
-            self._flat_plain.aggregate_and_step(
-                plain, pick(params, False), pick(moms, False), pick(index, False), hyper_dev
-            )
-            self.launches += self._flat_plain.launches
         if core.params:
             if core._native is None:
                 core._native = NativeCompressor(core)
@@ -787,5 +764,11 @@ class FusedSGDDriver:
             )
             core.step_counter += 1
             self.launches += core._native.launches
-        if joined is not None:
-            torch.cuda.current_stream().wait_event(joined)
+        plain = pick(grads, False)
+        if plain:
+            # after the low-rank path: a consumer that spins on its peers next to the product
+            # kernels (tried as a parallel side-stream branch) cost more than it hid
+            self._flat_plain.aggregate_and_step(
+                plain, pick(params, False), pick(moms, False), pick(index, False), hyper_dev
+            )
+            self.launches += self._flat_plain.launches
