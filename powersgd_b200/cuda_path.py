@@ -31,6 +31,23 @@ from .ops import layout, native
 from .utils import is_distributed, world_size
 
 
+class _Range:
+    """NVTX range when PSGD_B200_NVTX=1 (phase names show up in Nsight timelines); free otherwise."""
+
+    enabled = os.environ.get("PSGD_B200_NVTX", "0") == "1"
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if self.enabled:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if self.enabled:
+            torch.cuda.nvtx.range_pop()
+
+
 def _stream_ptr() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -438,16 +455,18 @@ class NativeCompressor:
                 out_side_i = self.h_loc[i] if sides[i] == left else self.h_in[i]
                 same.append(in_side_i)
                 other.append(out_side_i)
-            if t == 0 and self._early is not None:
-                # the first basis was orthonormalised on the side stream while forward / backward ran
-                early_side, event = self._early
-                self._early = None
-                torch.cuda.current_stream().wait_event(event)
-                if early_side != side:  # state changed under us (e.g. a checkpoint was loaded): redo
+            with _Range(f"psgd.iter{t}.orth"):
+                if t == 0 and self._early is not None:
+                    # the first basis was orthonormalised on the side stream while forward / backward ran
+                    early_side, event = self._early
+                    self._early = None
+                    torch.cuda.current_stream().wait_event(event)
+                    if early_side != side:  # state changed under us (e.g. a checkpoint was loaded): redo
+                        self._orth(side, state_in, self.h_in[t], same, self.cmat[t])
+                else:
                     self._orth(side, state_in, self.h_in[t], same, self.cmat[t])
-            else:
-                self._orth(side, state_in, self.h_in[t], same, self.cmat[t])
-            self._gemm(left, self.h_in[t], self.h_loc[t], other, self.cmat[t])
+            with _Range(f"psgd.iter{t}.product"):
+                self._gemm(left, self.h_in[t], self.h_loc[t], other, self.cmat[t])
             total = state_out.numel()
             if workers > 1 and self.comm is not None:
                 code = self.lib.psgd_factor_reduce_launch(
@@ -499,7 +518,8 @@ class NativeCompressor:
             self.h_sum = self.h_loc
         try:
             sides = self._half_iterations()
-            self._finalize(sides, fused_sgd=False, workers=workers)
+            with _Range("psgd.finalize"):
+                self._finalize(sides, fused_sgd=False, workers=workers)
         finally:
             if workers == 1:
                 self.h_sum = saved
@@ -525,7 +545,8 @@ class NativeCompressor:
             self.h_sum = self.h_loc
         try:
             sides = self._half_iterations()
-            self._finalize(sides, fused_sgd=True, workers=workers)
+            with _Range("psgd.finalize+sgd"):
+                self._finalize(sides, fused_sgd=True, workers=workers)
         finally:
             self._hyper_dev = keep
             if workers == 1:
