@@ -175,6 +175,17 @@ class PowerSGD(Aggregator):
                     return False
         return True
 
+    def close(self) -> None:
+        """Free multi-GPU resources (peer mappings, symmetric arenas). Call on every rank."""
+        native = self._powersgd._native
+        if native is not None:
+            native.close()
+        for flat in (getattr(self._allreduce, "_native", None), getattr(getattr(self, "_fused", None), "_flat_all", None),
+                     getattr(getattr(self, "_fused", None), "_flat_plain", None)):
+            if flat is not None and flat.comm is not None:
+                flat.comm.close()
+                flat.comm = None
+
     def begin_step(self) -> None:
         """Optional hint, called before forward: lets the native back end start the work of the
         coming aggregation that does not depend on the gradients (the first orthonormalisation)

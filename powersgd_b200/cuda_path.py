@@ -508,6 +508,12 @@ class NativeCompressor:
             done.record(self._side_stream)
         self._early = (side, done)
 
+    def close(self) -> None:
+        """Release the peer mappings and the symmetric arena (collective across ranks)."""
+        if self.comm is not None:
+            self.comm.close()
+            self.comm = None
+
     # -- public ----------------------------------------------------------------------------
     def aggregate(self, gradients: List[torch.Tensor]) -> List[torch.Tensor]:
         self.launches = 0
