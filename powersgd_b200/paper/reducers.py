@@ -31,6 +31,7 @@ import torch.distributed as dist
 
 from ..orthogonalization import gram_schmidt_
 from ..ops import signpack
+from ..ops.svd import svd_many
 from ..ops.topk import topk_abs
 from ..utils import TensorBuffer, n_bits
 from ..utils.timer import Timer
@@ -306,10 +307,12 @@ class AtomoReducer(Reducer):
 
     POISON = -10_000_000.0
 
-    def __init__(self, random_seed, device, timer=None, rank=1, svd_on_cpu=True):
+    def __init__(self, random_seed, device, timer=None, rank=1, svd_on_cpu=None):
         super().__init__(random_seed, device, timer)
         self.rank = rank
-        self.svd_on_cpu = svd_on_cpu
+        # the original always factorised on the CPU; on a CUDA device the batched native kernel
+        # is the default here (pass svd_on_cpu=True for the original behaviour)
+        self.svd_on_cpu = (torch.device(device).type != "cuda") if svd_on_cpu is None else svd_on_cpu
 
     @staticmethod
     def reshape_to_2d(tensor: torch.Tensor) -> torch.Tensor:
@@ -342,8 +345,12 @@ class AtomoReducer(Reducer):
     def reduce(self, grad_in, grad_out, memory_out) -> int:
         us, ss, vs = [], [], []
         with self.timer("reduce.encode", verbosity=2):
-            for tensor in grad_in:
-                u, s, v = self.svd(self.reshape_to_2d(tensor))
+            views = [self.reshape_to_2d(tensor) for tensor in grad_in]
+            if grad_in and grad_in[0].is_cuda and not self.svd_on_cpu:
+                factors = svd_many(views)  # narrow matrices: one native launch for all of them
+            else:
+                factors = [self.svd(m) for m in views]
+            for u, s, v in factors:
                 pick, probs = self.sample_singular_values(self.probabilities(s))
                 us.append(u[:, pick].contiguous())
                 vs.append(v[:, pick].contiguous())

@@ -54,3 +54,39 @@ def test_topk_abs_with_ties_and_zeros():
     assert (values.abs() == 2.0).all() and positions.long().unique().numel() == 150
     values, positions = topk_abs(x, 300)
     assert int((values.abs() == 2.0).sum()) == 200 and positions.long().unique().numel() == 300
+
+
+def test_batched_tall_svd_matches_torch():
+    from powersgd_b200.ops.svd import svd_many
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(0)
+    mats = [torch.randn(2048, 18, generator=g), torch.randn(32, 2, generator=g), torch.randn(10, 512, generator=g),
+            torch.randn(300, 32, generator=g), torch.randn(64, 64, generator=g)]
+    mats[3][:, 5] = mats[3][:, 4]  # a rank-deficient one
+    mats = [m.to(dev) for m in mats]
+    for m, (u, s, v) in zip(mats, svd_many(mats)):
+        k = min(m.shape)
+        assert u.shape == (m.shape[0], k) and v.shape == (m.shape[1], k) and s.shape == (k,)
+        assert (s[:-1] >= s[1:] - 1e-6).all()
+        ref = torch.linalg.svdvals(m)
+        assert torch.allclose(s, ref, rtol=1e-4, atol=1e-4 * ref[0].item())
+        recon = (u * s) @ v.t()
+        assert (recon - m).norm() / m.norm() < 1e-4
+        keep = s > 1e-4 * s[0]
+        eye = torch.eye(int(keep.sum()), device=dev)
+        assert torch.allclose(u[:, keep].t() @ u[:, keep], eye, atol=1e-3)
+        assert torch.allclose(v[:, keep].t() @ v[:, keep], eye, atol=1e-3)
+
+
+def test_atomo_reducer_on_gpu_uses_native_svd():
+    from powersgd_b200.paper import reducers as R
+
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    grads = [torch.randn(16, 8, 3, 3, device=dev), torch.randn(64, device=dev), torch.randn(10, 40, device=dev)]
+    outs, mems = [torch.zeros_like(g) for g in grads], [torch.zeros_like(g) for g in grads]
+    red = R.AtomoReducer(1, dev, None, rank=2)
+    assert red.svd_on_cpu is False
+    bits = red.reduce(grads, outs, mems)
+    assert bits > 0 and all(torch.isfinite(o).all() for o in outs)
