@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Headline benchmark: ResNet-18 (CIFAR stem) data-parallel training throughput with PowerSGD.
 
-Config (BASELINE.json, config 3): ResNet-18 with 3x3 stem and no max-pool (11.2 M parameters,
+Configuration: ResNet-18 with 3x3 stem and no max-pool (11.2 M parameters,
 BatchNorm), float32, synthetic 3x32x32 N(0,1) images with labels uniform over 10 classes,
 batch 128 per GPU, PowerSGD rank 2 with 2 half-iterations per step, SGD lr 0.1 with nesterov
 momentum 0.9 and weight decay 1e-4. One process per GPU; weak scaling.

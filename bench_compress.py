@@ -1,5 +1,5 @@
 #!/usr/bin/env python3
-"""Compression micro-benchmark (BASELINE config 2).
+"""Compression micro-benchmark (the second benchmark configuration).
 
 For float32 gradient matrices of the named shapes — each drawn as a rank-8 product of N(0,1)
 factors plus N(0, 1e-3) noise — time one `aggregate()` (compress + reduce + decompress +

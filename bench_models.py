@@ -1,5 +1,5 @@
 #!/usr/bin/env python3
-"""Throughput of the other benchmark configurations (BASELINE.json configs 4 and 5), same
+"""Throughput of the other benchmark configurations (the LSTM and GPT-2 configurations), same
 protocol and JSON line as bench.py (device-timed K steps after W warm-up steps, max over ranks,
 plus the end-to-end figure with pinned H2D input copies and a D2H loss read every step).
 

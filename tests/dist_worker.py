@@ -172,7 +172,7 @@ def scenario_train_step_graph():
 
 
 def scenario_mlp_gloo():
-    """BASELINE config 1: 2-layer MLP on CPU ranks; parameters stay bit-identical."""
+    """The plumbing configuration: 2-layer MLP on CPU ranks; parameters stay bit-identical."""
     rank, world, dev = _init("gloo")
     from powersgd_b200 import Config, PowerSGD, optimizer_step
 
