@@ -734,7 +734,7 @@ class FusedSGDDriver:
         """Host side of a step: momentum buffers, hyper-parameter table, async upload."""
         fresh = self._collect(optimizer)
         # the residual tensors may have been replaced (e.g. after loading a checkpoint)
-        if any(p.grad.data_ptr() != g.data_ptr() for p, g in zip(self._params[:4], self._grads[:4])):
+        if any(p.grad.data_ptr() != g.data_ptr() for p, g in zip(self._params, self._grads)):
             self._grads = [p.grad.data for p in self._params]
         groups = optimizer.param_groups
         table = np.zeros(len(groups), dtype=layout.HYPER_DTYPE)

@@ -78,6 +78,14 @@ class TrainStep:
         begin = getattr(self.aggregator, "begin_step", None)
         if begin is not None:
             begin()
+        # Tensors that are all-reduced uncompressed leave no residual (their .grad is all zeros
+        # after a step), so autograd does not need to ACCUMULATE onto it: dropping the zero tensor
+        # lets it adopt the fresh gradient and saves one small add kernel per such tensor.
+        mask = getattr(self.aggregator, "is_compressed_mask", None)
+        if mask is not None and getattr(self.aggregator, "compressing", False):
+            for p, keep in zip(self._params(), mask):
+                if not keep:
+                    p.grad = None
 
     def _eager(self, x: torch.Tensor, y: torch.Tensor, time_aggregate: bool = False) -> torch.Tensor:
         self._begin()
