@@ -733,9 +733,6 @@ class FusedSGDDriver:
     def prepare(self, optimizer) -> None:
         """Host side of a step: momentum buffers, hyper-parameter table, async upload."""
         fresh = self._collect(optimizer)
-        # the residual tensors may have been replaced (e.g. after loading a checkpoint)
-        if any(p.grad.data_ptr() != g.data_ptr() for p, g in zip(self._params, self._grads)):
-            self._grads = [p.grad.data for p in self._params]
         groups = optimizer.param_groups
         table = np.zeros(len(groups), dtype=layout.HYPER_DTYPE)
         for gi, group in enumerate(groups):
@@ -770,6 +767,10 @@ class FusedSGDDriver:
     def step(self, optimizer, prepared: bool = False) -> None:
         if not prepared:
             self.prepare(optimizer)
+        # the gradient tensors may have been replaced since the last step (dropped zero gradients
+        # re-created by autograd, a loaded checkpoint): always bind what the parameters hold now
+        if any(p.grad.data_ptr() != g.data_ptr() for p, g in zip(self._params, self._grads)):
+            self._grads = [p.grad.data for p in self._params]
         agg = self.agg
         hyper_dev, index, params, moms, grads = self._hyper_dev, self._index, self._params, self._moms, self._grads
         if len(grads) != len(agg.is_compressed_mask):
