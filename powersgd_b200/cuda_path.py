@@ -64,8 +64,23 @@ def _ptr_array(tensors: Sequence[torch.Tensor]):
 
 
 def _to_device(array: np.ndarray, device: torch.device) -> torch.Tensor:
-    raw = torch.from_numpy(np.ascontiguousarray(array).view(np.uint8).reshape(-1).copy())
-    return raw.to(device, non_blocking=False)
+    """Upload a descriptor table. Staged through pinned memory with an async copy on the current
+    stream, so that it is legal during CUDA-graph capture (where it becomes a copy node that
+    re-reads the pinned buffer on every replay; the buffer is kept alive with the result)."""
+    raw = np.ascontiguousarray(array).view(np.uint8).reshape(-1)
+    pinned = torch.empty(max(raw.size, 1), dtype=torch.uint8).pin_memory()
+    pinned.numpy()[: raw.size] = raw
+    out = torch.empty(max(raw.size, 1), dtype=torch.uint8, device=device)
+    out.copy_(pinned, non_blocking=True)
+    out._psgd_pinned_src = pinned
+    if torch.cuda.is_current_stream_capturing():
+        # the recorded copy node reads `pinned` and writes `out` on every replay: both must
+        # outlive whatever later rebinding drops them from their owner
+        _CAPTURED_TABLES.append((out, pinned))
+    return out
+
+
+_CAPTURED_TABLES: list = []
 
 
 def _split_even(total: int, max_chunk: int, multiple: int) -> List[Tuple[int, int]]:
@@ -609,8 +624,8 @@ class NativeFlatAllReduce:
                 block_first.append(first)
             cursor += g.numel()
         self._items_dev = _to_device(items, device)
-        self._block_item = torch.tensor(block_item, dtype=torch.int32, device=device)
-        self._block_first = torch.tensor(block_first, dtype=torch.int32, device=device)
+        self._block_item = _to_device(np.asarray(block_item, dtype=np.int32), device)
+        self._block_first = _to_device(np.asarray(block_first, dtype=np.int32), device)
         self._nblocks = len(block_item)
         self._views = views
         self._hyper_dev = _to_device(NativeCompressor._default_hyper(), device)

@@ -141,7 +141,8 @@ class TrainStep:
         saved = (agg.step_counter, agg._powersgd.step_counter)
         graph = torch.cuda.CUDAGraph()
         torch.cuda.synchronize()
-        with torch.cuda.graph(graph, pool=self._pool):
+        # relaxed: descriptor tables rebuilt during capture allocate pinned staging memory
+        with torch.cuda.graph(graph, pool=self._pool, capture_error_mode="relaxed"):
             self._begin()
             loss = self.loss_fn(self.model(self._static_x), self._static_y)
             loss.backward()
