@@ -37,7 +37,6 @@ struct GemmArgs {
   // Multi-GPU: the epilogue also pushes every finished factor element, tagged with the next
   // epoch, into slot[rank] of every peer's arena. Null for a single worker.
   const PsgdCommDev* comm;
-  int expected_ctas;
 };
 
 template <int RT>
@@ -306,7 +305,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nn_kernel(GemmArgs a) 
 // ------------------------------------------------------------------------------------------
 static void fill_args(GemmArgs& a, const void* mats, const void* tiles, const float* in, float* out, int ncorr,
                       const float* const* corr_fac, const float* const* corr_c, float* partial, int* tickets,
-                      const void* comm, int expected_ctas) {
+                      const void* comm) {
   a.mats = (const PsgdMat*)mats;
   a.tiles = (const PsgdTile*)tiles;
   a.in = in;
@@ -319,7 +318,6 @@ static void fill_args(GemmArgs& a, const void* mats, const void* tiles, const fl
   a.partial = partial;
   a.tickets = tickets;
   a.comm = (const PsgdCommDev*)comm;
-  a.expected_ctas = expected_ctas;
 }
 
 template <int RT, int VEC>
@@ -367,14 +365,14 @@ PSGD_API int psgd_gemm_template_rank(int max_r) {
 PSGD_API int psgd_gemm_ffma_launch(int transposed, int vec4, int max_r, const void* mats, const void* tiles,
                                    int ntiles, const float* in, float* out, int ncorr,
                                    const float* const* corr_fac, const float* const* corr_c, float* partial,
-                                   int* tickets, const void* comm, int expected_ctas, cudaStream_t stream) {
+                                   int* tickets, const void* comm, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
   if (max_r > PSGD_MAX_RANK || ncorr > PSGD_MAX_HIST) {
     psgd_set_error("psgd_gemm_ffma_launch: rank %d or history %d beyond the compiled maximum", max_r, ncorr);
     return -1;
   }
   GemmArgs a;
-  fill_args(a, mats, tiles, in, out, ncorr, corr_fac, corr_c, partial, tickets, comm, expected_ctas);
+  fill_args(a, mats, tiles, in, out, ncorr, corr_fac, corr_c, partial, tickets, comm);
   if (transposed) {
     if (vec4) { PSGD_DISPATCH_RT(launch_nt, 4) } else { PSGD_DISPATCH_RT(launch_nt, 1) }
   } else {

@@ -53,7 +53,6 @@ struct TcArgs {
   float* partial;
   int* tickets;
   const PsgdCommDev* comm;
-  int expected_ctas;
   int* status;               // device word, set on a wait that ran out
 };
 
@@ -473,7 +472,7 @@ PSGD_API int psgd_tma_encode_matrix(void* out, const float* base, int n, int m) 
 PSGD_API int psgd_gemm_tc_launch(int transposed, int split, int max_r, const void* mats, const void* tiles, int ntiles,
                                  const void* maps, const float* in, float* out, int ncorr,
                                  const float* const* corr_fac, const float* const* corr_c, float* partial,
-                                 int* tickets, const void* comm, int expected_ctas, int* status, cudaStream_t stream) {
+                                 int* tickets, const void* comm, int* status, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
   if (max_r > PSGD_MAX_RANK || ncorr > PSGD_MAX_HIST) {
     psgd_set_error("psgd_gemm_tc_launch: rank %d or history %d beyond the compiled maximum", max_r, ncorr);
@@ -493,7 +492,6 @@ PSGD_API int psgd_gemm_tc_launch(int transposed, int split, int max_r, const voi
   a.partial = partial;
   a.tickets = tickets;
   a.comm = (const PsgdCommDev*)comm;
-  a.expected_ctas = expected_ctas;
   a.status = status;
   if (transposed) return split ? dispatch_rank<true, true>(a, max_r, ntiles, stream) : dispatch_rank<true, false>(a, max_r, ntiles, stream);
   return split ? dispatch_rank<false, true>(a, max_r, ntiles, stream) : dispatch_rank<false, false>(a, max_r, ntiles, stream);

@@ -21,7 +21,6 @@ void psgd_set_error(const char* fmt, ...);
 // Status word written by kernels whose waits ran out. 0 = fine.
 enum PsgdStatus : int {
   PSGD_OK = 0,
-  PSGD_TIMEOUT_GRID_BARRIER = 1,
   PSGD_TIMEOUT_PEER_BARRIER = 2,
   PSGD_TIMEOUT_MBARRIER = 3,
   PSGD_BAD_ARGUMENT = 4,
@@ -45,24 +44,6 @@ __device__ __forceinline__ double psgd_warp_sum(double v) {
   return v;
 }
 
-__device__ __forceinline__ int psgd_ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void psgd_st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int psgd_ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ int psgd_atom_add_release_gpu(int* p, int v) {
-  int old;
-  asm volatile("atom.add.release.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
-  return old;
-}
 __device__ __forceinline__ int psgd_atom_add_acqrel_gpu(int* p, int v) {
   int old;
   asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");

@@ -3,8 +3,9 @@
 Per optimizer step the reference issues several hundred small PyTorch ops
 (powersgd/powersgd.py:146-235). Here a step is, for T half-iterations:
 
-    T x [ orthonormalise (1 launch) -> grouped product (1-2 launches) -> all-reduce of the
-          fresh factor ]  ->  decompress + error feedback (+ SGD) (1-2 launches)
+    T x [ orthonormalise (1 launch) -> grouped product (1-2 launches; multi-GPU: its epilogue
+          pushes the fresh factor to every peer) -> sum of the peers' slots (1 small launch) ]
+      ->  decompress + error feedback (+ SGD) (1-2 launches)
 
 over ALL shape groups at once. The gradient matrices are addressed in place through a
 pointer table (no `torch.stack`, no un-batching copies), the deflation between half-iterations
@@ -118,10 +119,6 @@ class TilePlan:
         self.nn_cols_cap = 1024
         self.rp_tc = lib.psgd_gemm_tc_rank_pad(self.max_r)
         self.fin_tc_ok = False  # set by the compressor: (half-iterations x rank) fits the tensor-core finalize
-
-    def vec_ok(self, mi: int) -> bool:
-        g = self.plan.groups[self.mats[mi][0]]
-        return g.m % 4 == 0
 
     def build(self, vec_flags: Sequence[bool], tc_flags: Optional[Sequence[bool]] = None):
         """Tile arrays split by vector width (CUDA-core kernels: keys 4 and 1) and, for the
@@ -351,7 +348,6 @@ class NativeCompressor:
 
     def _gemm(self, transposed: bool, fin: torch.Tensor, fout: torch.Tensor, corr_fac, corr_c):
         name = "nt" if transposed else "nn"
-        expected = sum(self._tiles_dev[name][v][1] for v in (4, 1, "tc"))
         tiles, count = self._tiles_dev[name]["tc"]
         if count:
             code = self.lib.psgd_gemm_tc_launch(
@@ -370,7 +366,6 @@ class NativeCompressor:
                 _ptr(self._partial_tc),
                 _ptr(self._tickets),
                 self.comm.ptr if self.comm is not None else ctypes.c_void_p(0),
-                expected,
                 _ptr(self._tc_status),
                 _stream_ptr(),
             )
@@ -395,7 +390,6 @@ class NativeCompressor:
                 _ptr(self._partial),
                 _ptr(self._tickets),
                 self.comm.ptr if self.comm is not None else ctypes.c_void_p(0),
-                expected,
                 _stream_ptr(),
             )
             native.check(code, "psgd_gemm_ffma_launch")

@@ -44,7 +44,7 @@ def _regular_entry_point(lib, M, P, r):
         1, 1 if vec else 0, r, ctypes.c_void_p(desc_dev.data_ptr()), ctypes.c_void_p(tile_dev.data_ptr()), len(tile_arr),
         ctypes.c_void_p(P.data_ptr()), ctypes.c_void_p(Q.data_ptr()), 0, ctypes.cast(empty, ctypes.c_void_p),
         ctypes.cast(empty, ctypes.c_void_p), ctypes.c_void_p(partial.data_ptr()), ctypes.c_void_p(tickets.data_ptr()),
-        null, 0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
+        null, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
     )
     assert code == 0, lib.psgd_last_error()
     torch.cuda.synchronize()
