@@ -94,6 +94,9 @@ def time_aggregate(make_agg, grads, steps, warmup, flush, world, device):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     err = sum(float(w.double().norm() ** 2) for w in work) ** 0.5
+    close = getattr(agg, "close", None)
+    if close is not None:
+        close()  # symmetric arenas are returned now, not when the collector gets to them
     return ms, err, out
 
 
@@ -166,6 +169,22 @@ def main():
                         t = torch.tensor([sum(ts) / len(ts)], device=device, dtype=torch.float64)
                         dist.all_reduce(t, op=dist.ReduceOp.MAX)
                         row["uncompressed_allreduce_ms"] = float(t.item())
+                        # the same mean through this library's peer-store kernels (pack + push, owner
+                        # sum + push, consume), which can be recorded in a CUDA graph
+                        from powersgd_b200.cuda_path import NativeFlatAllReduce
+
+                        class _Flat:
+                            def __init__(self):
+                                self.red = NativeFlatAllReduce()
+
+                            def aggregate(self, tensors):
+                                return self.red.aggregate(tensors)
+
+                            def close(self):
+                                self.red.close()
+
+                        flat_ms, _, _ = time_aggregate(_Flat, grads, args.steps, args.warmup, flush, world, device)
+                        row["uncompressed_peer_store_allreduce_ms"] = flat_ms
                 if rank == 0:
                     print(json.dumps(row), flush=True)
         del grads, flush

@@ -297,6 +297,12 @@ class BasicPowerSGD(Aggregator):
         self.step_counter += 1
         return outputs
 
+    def close(self) -> None:
+        """Free multi-GPU resources of the native back end (symmetric arenas). Call on every rank."""
+        if self._native is not None:
+            self._native.close()
+            self._native = None
+
     def _aggregate_torch(self, gradients: List[torch.Tensor]) -> List[torch.Tensor]:
         plan, iters = self.plan, self.config.num_iters_per_step
         mats = [view_as_matrix(g) for g in gradients]

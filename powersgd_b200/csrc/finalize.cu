@@ -243,11 +243,31 @@ struct FlatArgs {
              // 3: local (no communication): out = grad / divisor, grad = 0 ; 4: local + SGD
              // 5: pack + push {value, epoch} words to every peer's slot (in-kernel all-reduce, part 1)
              // 6: poll the own slots, sum them in rank order -> out ; 7: same + SGD (part 2)
+             // large buffers go two-shot (mode 0, then psgd_bulk_allreduce_launch on `flat`, which
+             // is the data region of the arena, then one of):
+             // 12: wait for the gathered chunks this block reads, then unpack ; 13: same + SGD
   const PsgdCommDev* comm;
+  long long n_pad;  // modes 12, 13: length of the arena's data region (whole chunks per rank)
 };
 
 constexpr int FLAT_THREADS = 256;
 constexpr int FLAT_PER_BLOCK = FLAT_THREADS * 8;
+
+// Modes 12, 13: wait for the chunks of the flat index range [g0, g1) that peers gather into this
+// rank's data region. Slices are whole chunks, so chunk `lin` belongs to owner lin / cps; the own
+// slice was written by this rank's earlier kernel. A block spans at most two chunks.
+__device__ __forceinline__ void flat_wait_gathered(const FlatArgs& a, const PsgdCommDev& c, int e1, long long g0, long long g1) {
+  PsgdBulk b;
+  b.comm = a.comm;
+  b.n_pad = a.n_pad;
+  b.cps = (int)(a.n_pad / c.world / PSGD_BULK_CHUNK);
+  const int lin0 = (int)(g0 / PSGD_BULK_CHUNK), lin1 = (int)((g1 - 1) / PSGD_BULK_CHUNK);
+  if ((int)threadIdx.x <= lin1 - lin0) {
+    const int lin = lin0 + threadIdx.x, owner = lin / b.cps;
+    if (owner != c.rank) psgd_flag_wait(c, psgd_bulk_flag(c, b, c.rank, 1, owner, lin % b.cps), e1);
+  }
+  __syncthreads();
+}
 
 __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
   const PsgdFlat it = a.items[a.block_item[blockIdx.x]];
@@ -260,6 +280,8 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
     e1 = *c.epoch + 1;
   }
   bool ok = true;
+  if (a.mode >= 12)
+    flat_wait_gathered(a, c, e1, it.flat_off + first, it.flat_off + min((long long)it.numel, first + (long long)FLAT_PER_BLOCK));
   for (int e = threadIdx.x; e < FLAT_PER_BLOCK; e += FLAT_THREADS) {
     const long long i = first + e;
     if (i >= it.numel) break;
@@ -275,13 +297,15 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
       continue;
     } else if (a.mode == 1 || a.mode == 2) {
       g = a.flat[it.flat_off + i];
+    } else if (a.mode >= 12) {
+      g = __ldcg(a.flat + it.flat_off + i);  // written by peers: never through L1
     } else if (a.mode >= 6) {
       g = psgd_comm_reduce(c, e1, it.flat_off + i, ok);
     } else {
       g = it.grad[i] / a.divisor;
       it.grad[i] = 0.f;
     }
-    if (a.mode == 2 || a.mode == 4 || a.mode == 7) {
+    if (a.mode == 2 || a.mode == 4 || a.mode == 7 || a.mode == 13) {
       float p = it.param[i];
       float mo = h.has_momentum ? it.mom[i] : 0.f;
       psgd_sgd_update(g, p, &mo, h);
@@ -294,14 +318,122 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
   if (a.mode >= 6) psgd_comm_close_epoch(c, e1);  // the last consumer CTA advances the channel
 }
 
+// Streaming variant of the modes that move whole buffers (0-4, 12, 13): four elements per access.
+// The host selects it when every pointer of every item is 16-byte aligned (flat offsets always
+// are: items start at multiples of four floats); the ragged end of an item goes element-wise.
+template <int MODE>
+__device__ __forceinline__ void flat_one(const FlatArgs& a, const PsgdFlat& it, const PsgdHyper& h, long long i) {
+  float g;
+  if (MODE == 0) {
+    a.flat[it.flat_off + i] = it.grad[i] / a.divisor;
+    it.grad[i] = 0.f;
+    return;
+  } else if (MODE == 1 || MODE == 2) {
+    g = a.flat[it.flat_off + i];
+  } else if (MODE >= 12) {
+    g = __ldcg(a.flat + it.flat_off + i);
+  } else {
+    g = it.grad[i] / a.divisor;
+    it.grad[i] = 0.f;
+  }
+  if (MODE == 2 || MODE == 4 || MODE == 13) {
+    float p = it.param[i];
+    float mo = h.has_momentum ? it.mom[i] : 0.f;
+    psgd_sgd_update(g, p, &mo, h);
+    it.param[i] = p;
+    if (h.has_momentum) it.mom[i] = mo;
+  } else {
+    it.out[i] = g;
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_vec_kernel(FlatArgs a) {
+  const PsgdFlat it = a.items[a.block_item[blockIdx.x]];
+  const long long first = a.block_first[blockIdx.x];
+  const PsgdHyper h = a.hyper[it.hyper];
+  const long long left = min((long long)it.numel - first, (long long)FLAT_PER_BLOCK);
+  PsgdCommDev c;
+  int e1 = 0;
+  if (MODE >= 12) {
+    c = *a.comm;
+    e1 = *c.epoch + 1;
+    flat_wait_gathered(a, c, e1, it.flat_off + first, it.flat_off + first + left);
+  }
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  constexpr int GROUPS = FLAT_PER_BLOCK / 4 / FLAT_THREADS;
+#pragma unroll
+  for (int k = 0; k < GROUPS; ++k) {
+    const int e = (threadIdx.x + k * FLAT_THREADS) * 4;
+    if (e >= left) break;
+    const long long i = first + e;
+    if (e + 4 > left) {
+      for (int j = 0; e + j < left; ++j) flat_one<MODE>(a, it, h, i + j);
+      break;
+    }
+    float4 g;
+    float4* grad4 = (float4*)(it.grad + i);
+    float4* flat4 = (float4*)(a.flat + it.flat_off + i);
+    if (MODE == 0 || MODE == 3 || MODE == 4) {
+      g = *grad4;
+      // the scalar path divides; a multiplication by the reciprocal differs in the last bit for
+      // divisors that are not powers of two, so divide here too
+      g.x /= a.divisor; g.y /= a.divisor; g.z /= a.divisor; g.w /= a.divisor;
+      *grad4 = zero4;
+      if (MODE == 0) {
+        *flat4 = g;
+        continue;
+      }
+    } else if (MODE >= 12) {
+      g = __ldcg(flat4);
+    } else {
+      g = *flat4;
+    }
+    if (MODE == 2 || MODE == 4 || MODE == 13) {
+      float4* p4 = (float4*)(it.param + i);
+      float4 p = *p4;
+      if (h.has_momentum) {
+        float4* m4 = (float4*)(it.mom + i);
+        float4 mo = *m4;
+        psgd_sgd_update(g.x, p.x, &mo.x, h);
+        psgd_sgd_update(g.y, p.y, &mo.y, h);
+        psgd_sgd_update(g.z, p.z, &mo.z, h);
+        psgd_sgd_update(g.w, p.w, &mo.w, h);
+        *m4 = mo;
+      } else {
+        float4 mo = zero4;
+        psgd_sgd_update(g.x, p.x, &mo.x, h);
+        psgd_sgd_update(g.y, p.y, &mo.y, h);
+        psgd_sgd_update(g.z, p.z, &mo.z, h);
+        psgd_sgd_update(g.w, p.w, &mo.w, h);
+      }
+      *p4 = p;
+    } else {
+      *(float4*)(it.out + i) = g;
+    }
+  }
+  if (MODE >= 12) psgd_comm_close_epoch(c, e1);
+}
+
 PSGD_API int psgd_flat_block_elems() { return FLAT_PER_BLOCK; }
 
-PSGD_API int psgd_flat_launch(int mode, const void* items, const int* block_item, const int* block_first,
+template <int MODE>
+static void flat_vec_launch(const FlatArgs& a, int nblocks, cudaStream_t stream) {
+  psgd_flat_vec_kernel<MODE><<<nblocks, FLAT_THREADS, 0, stream>>>(a);
+}
+
+// vec != 0 promises 16-byte aligned grad / param / mom / out pointers and flat offsets that are
+// multiples of four floats; modes 5-7 (flag-in-data words) always run element-wise.
+PSGD_API int psgd_flat_launch(int mode, int vec, const void* items, const int* block_item, const int* block_first,
                               int nblocks, const void* hyper, float* flat, float divisor, const void* comm,
-                              cudaStream_t stream) {
+                              long long n_pad, cudaStream_t stream) {
   if (nblocks <= 0) return 0;
   if (mode >= 5 && comm == nullptr) {
     psgd_set_error("psgd_flat_launch: mode %d needs a communication channel", mode);
+    return -1;
+  }
+  if (!((mode >= 0 && mode <= 7) || mode == 12 || mode == 13)) {
+    psgd_set_error("psgd_flat_launch: unknown mode %d", mode);
     return -1;
   }
   FlatArgs a;
@@ -313,7 +445,20 @@ PSGD_API int psgd_flat_launch(int mode, const void* items, const int* block_item
   a.divisor = divisor;
   a.mode = mode;
   a.comm = (const PsgdCommDev*)comm;
-  psgd_flat_kernel<<<nblocks, FLAT_THREADS, 0, stream>>>(a);
+  a.n_pad = n_pad;
+  if (vec && !(mode >= 5 && mode <= 7)) {
+    switch (mode) {
+      case 0: flat_vec_launch<0>(a, nblocks, stream); break;
+      case 1: flat_vec_launch<1>(a, nblocks, stream); break;
+      case 2: flat_vec_launch<2>(a, nblocks, stream); break;
+      case 3: flat_vec_launch<3>(a, nblocks, stream); break;
+      case 4: flat_vec_launch<4>(a, nblocks, stream); break;
+      case 12: flat_vec_launch<12>(a, nblocks, stream); break;
+      default: flat_vec_launch<13>(a, nblocks, stream); break;
+    }
+  } else {
+    psgd_flat_kernel<<<nblocks, FLAT_THREADS, 0, stream>>>(a);
+  }
   PSGD_CUDA_OK(cudaGetLastError());
   return 0;
 }

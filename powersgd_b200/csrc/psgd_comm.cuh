@@ -87,3 +87,59 @@ __device__ __forceinline__ void psgd_comm_close_epoch(const PsgdCommDev& c, int 
     }
   }
 }
+
+// ---- bulk protocol (large messages) ---------------------------------------------------------
+// The flag-in-data words double the bytes on the wire. Messages of megabytes travel as plain
+// floats instead, in chunks; the CTA that wrote a chunk fences once (thread 0, after a CTA
+// barrier) and then publishes the epoch in one flag per chunk. With a thousand CTAs in flight the
+// fence latency (a round trip over the link) overlaps other CTAs' stores. Flags only grow, so
+// they are never reset; chunk data is read with L1-bypassing loads after the acquire.
+__device__ __forceinline__ void psgd_flag_publish(int32_t* flag, int epoch) {
+  asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+}
+
+__device__ __forceinline__ int psgd_flag_peek(const int32_t* flag) {
+  int v;
+  asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+  return v;
+}
+
+// Bounded wait until *flag == epoch. False when the wait was abandoned (now or earlier).
+__device__ __forceinline__ bool psgd_flag_wait(const PsgdCommDev& c, const int32_t* flag, int epoch) {
+  if (psgd_flag_peek(flag) == epoch) return true;
+  const uint64_t t0 = psgd_globaltimer_ns();
+  int spins = 0;
+  while (true) {
+    if (psgd_flag_peek(flag) == epoch) return true;
+    __nanosleep(64);
+    if ((++spins & 63) == 0) {
+      if (*((volatile int*)c.abort_flag) != 0) return false;
+      if (psgd_globaltimer_ns() - t0 > c.timeout_ns) {
+        *((volatile int*)c.abort_flag) = 1;
+        *((volatile int*)c.status) = PSGD_TIMEOUT_PEER_BARRIER;
+        __threadfence_system();
+        return false;
+      }
+    }
+  }
+}
+
+constexpr int PSGD_BULK_CHUNK = 4096;  // floats per chunk; slices are padded to whole chunks
+
+// Where the parts of a bulk all-reduce live inside every rank's arena (byte offsets are multiples
+// of 256): the flat data itself, the landing area of the reduce-scatter, and the two flag tables.
+typedef struct {
+  const PsgdCommDev* comm;
+  long long n_pad;      // floats, a multiple of world * PSGD_BULK_CHUNK
+  int cps;              // chunks per slice = n_pad / world / PSGD_BULK_CHUNK
+} PsgdBulk;
+
+__device__ __forceinline__ float* psgd_bulk_data(const PsgdCommDev& c, int peer) { return (float*)c.slots[peer]; }
+__device__ __forceinline__ float* psgd_bulk_stage(const PsgdCommDev& c, const PsgdBulk& b, int peer) {
+  return (float*)c.slots[peer] + b.n_pad;
+}
+// which = 0: "rank src pushed chunk q of my slice"; 1: "owner src wrote chunk q of its slice here"
+__device__ __forceinline__ int32_t* psgd_bulk_flag(const PsgdCommDev& c, const PsgdBulk& b, int peer, int which, int src, int q) {
+  return (int32_t*)((float*)c.slots[peer] + 2 * b.n_pad) + ((long long)which * c.world + src) * b.cps + q;
+}
+

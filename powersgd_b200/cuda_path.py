@@ -573,14 +573,21 @@ class NativeFlatAllReduce:
     scale, the zeroing of the inputs and (optionally) the SGD update done by one multi-tensor
     kernel on each side of the collective."""
 
-    # one-shot pushes send (W-1) copies of the buffer; above this arena size use the library ring
-    P2P_ARENA_LIMIT_BYTES = 1 << 30
+    # one-shot pushes send (W-1) copies of the buffer: right for the small per-step buffers
+    # (latency of one hop). Larger ones (whole models: the plain all-reduce aggregator, the
+    # un-compressed warm-up phase) go two-shot: reduce-scatter + all-gather through peer stores,
+    # 2 (W-1)/W copies. Beyond the arena limit the library ring takes over (eager only).
+    ONE_SHOT_LIMIT_FLOATS = 1 << 18
+    P2P_ARENA_LIMIT_BYTES = 8 << 30
 
     def __init__(self):
         self.lib = native.lib()
         self._key = None
         self.launches = 0
         self.comm = None
+        self.path = "local"
+        self.n_pad = 0
+        self._bulk_layout = None
 
     def _bind(self, grads, params=None, moms=None, hyper_index=None, need_out=True):
         key = (
@@ -592,8 +599,9 @@ class NativeFlatAllReduce:
         if key == self._key:
             return
         device = grads[0].device
-        total = sum(g.numel() for g in grads)
-        self._flat = torch.empty(total, device=device, dtype=torch.float32)
+        # every tensor starts at a multiple of four floats in the flat buffer (16-byte accesses)
+        total = sum(-(-g.numel() // 4) * 4 for g in grads)
+        self._flat = torch.zeros(total, device=device, dtype=torch.float32)
         self._out = torch.empty(total, device=device, dtype=torch.float32) if need_out else None
         items = np.zeros(len(grads), dtype=layout.FLAT_DTYPE)
         per_block = self.lib.psgd_flat_block_elems()
@@ -616,7 +624,9 @@ class NativeFlatAllReduce:
             for first in range(0, g.numel(), per_block):
                 block_item.append(i)
                 block_first.append(first)
-            cursor += g.numel()
+            cursor += -(-g.numel() // 4) * 4
+        pointers = [int(items[name][i]) for name in ("grad", "param", "mom", "out") for i in range(len(grads))]
+        self._vec = 1 if all(ptr % 16 == 0 for ptr in pointers) else 0
         self._items_dev = _to_device(items, device)
         self._block_item = _to_device(np.asarray(block_item, dtype=np.int32), device)
         self._block_first = _to_device(np.asarray(block_first, dtype=np.int32), device)
@@ -624,23 +634,49 @@ class NativeFlatAllReduce:
         self._views = views
         self._hyper_dev = _to_device(NativeCompressor._default_hyper(), device)
         self._key = key
-        workers = world_size()
-        if self.comm is not None and self.comm.cap < total:
+        self._choose_path(total, world_size())
+
+    def _choose_path(self, total: int, workers: int) -> None:
+        """local | oneshot (flag-in-data words to every peer) | bulk (two-shot, plain floats +
+        chunk flags; the flat buffer lives in the symmetric arena; PSGD_B200_FLAT=bulk forces it
+        for small buffers too) | nccl (PSGD_B200_COMM=nccl, or arena too large)."""
+        want = os.environ.get("PSGD_B200_FLAT", "auto")
+        p2p = workers > 1 and os.environ.get("PSGD_B200_COMM", "p2p") == "p2p"
+        self.n_pad = total
+        if workers == 1:
+            path, cap = "local", 0
+        elif not p2p:
+            path, cap = "nccl", 0
+        elif total <= self.ONE_SHOT_LIMIT_FLOATS and want != "bulk":
+            path, cap = "oneshot", total
+        else:
+            unit = workers * int(self.lib.psgd_bulk_chunk_floats())
+            self.n_pad = -(-total // unit) * unit
+            nbytes = int(self.lib.psgd_bulk_arena_bytes(ctypes.c_longlong(self.n_pad), workers))
+            path, cap = "bulk", -(-nbytes // (16 * workers))
+        if cap and 2 * workers * cap * 8 > self.P2P_ARENA_LIMIT_BYTES:
+            path, cap = "nccl", 0
+        # An arena is reused only under the discipline it was written with: flag-in-data words of
+        # old epochs never match a new one, but the bulk layout puts its flag tables where another
+        # layout had data, so a change of protocol or of the bulk size starts from a zeroed arena.
+        bulk_layout = self.n_pad if path == "bulk" else None
+        if self.comm is not None and (self.comm.cap < cap or cap == 0 or bulk_layout != self._bulk_layout):
             self.comm.close()
             self.comm = None
-        if (
-            workers > 1
-            and self.comm is None
-            and os.environ.get("PSGD_B200_COMM", "p2p") == "p2p"
-            and 2 * workers * total * 8 <= self.P2P_ARENA_LIMIT_BYTES
-        ):
+        self._bulk_layout = bulk_layout
+        if cap and self.comm is None:
             from .parallel.symm import Channel
 
-            self.comm = Channel(total)
+            self.comm = Channel(cap)
+        if path == "bulk":
+            # pack writes and unpack reads the arena's data region directly
+            self._flat = self.comm.slots.tensor(0, self.n_pad)
+        self.path = path
 
     def _launch(self, mode: int, hyper_dev: torch.Tensor, divisor: float) -> None:
         code = self.lib.psgd_flat_launch(
             mode,
+            self._vec,
             _ptr(self._items_dev),
             _ptr(self._block_item),
             _ptr(self._block_first),
@@ -649,39 +685,47 @@ class NativeFlatAllReduce:
             _ptr(self._flat),
             float(divisor),
             self.comm.ptr if self.comm is not None else ctypes.c_void_p(0),
+            ctypes.c_longlong(self.n_pad),
             _stream_ptr(),
         )
         native.check(code, "psgd_flat_launch")
         self.launches += 1
 
+    def _run(self, hyper_dev: torch.Tensor, workers: int, sgd: bool) -> None:
+        if self.path == "local":
+            self._launch(4 if sgd else 3, hyper_dev, 1.0)
+        elif self.path == "bulk":
+            self._launch(0, hyper_dev, float(workers))
+            code = self.lib.psgd_bulk_allreduce_launch(self.comm.ptr, ctypes.c_longlong(self.n_pad), workers, _stream_ptr())
+            native.check(code, "psgd_bulk_allreduce_launch")
+            self.launches += 2
+            self._launch(13 if sgd else 12, hyper_dev, 1.0)
+        elif self.path == "oneshot":
+            self._launch(5, hyper_dev, float(workers))
+            self._launch(7 if sgd else 6, hyper_dev, 1.0)
+        else:
+            self._launch(0, hyper_dev, float(workers))
+            dist.all_reduce(self._flat)
+            self._launch(2 if sgd else 1, hyper_dev, 1.0)
+
     def aggregate(self, gradients: List[torch.Tensor]) -> List[torch.Tensor]:
         self.launches = 0
         self._bind(gradients)
-        workers = world_size()
-        if workers == 1:
-            self._launch(3, self._hyper_dev, 1.0)
-        elif self.comm is not None:
-            self._launch(5, self._hyper_dev, float(workers))
-            self._launch(6, self._hyper_dev, 1.0)
-        else:
-            self._launch(0, self._hyper_dev, float(workers))
-            dist.all_reduce(self._flat)
-            self._launch(1, self._hyper_dev, 1.0)
+        self._run(self._hyper_dev, world_size(), sgd=False)
         return list(self._views)
 
     def aggregate_and_step(self, gradients, params, moms, hyper_index, hyper_dev) -> None:
         self.launches = 0
         self._bind(gradients, params, moms, hyper_index, need_out=False)
-        workers = world_size()
-        if workers == 1:
-            self._launch(4, hyper_dev, 1.0)
-        elif self.comm is not None:
-            self._launch(5, hyper_dev, float(workers))
-            self._launch(7, hyper_dev, 1.0)
-        else:
-            self._launch(0, hyper_dev, float(workers))
-            dist.all_reduce(self._flat)
-            self._launch(2, hyper_dev, 1.0)
+        self._run(hyper_dev, world_size(), sgd=True)
+
+    def close(self) -> None:
+        """Release the symmetric arena (collective across ranks)."""
+        if self.comm is not None:
+            self.comm.close()
+            self.comm = None
+        self._key = None
+        self._bulk_layout = None
 
 
 class FusedSGDDriver:

@@ -31,7 +31,7 @@ def declare(lib) -> None:
     lib.psgd_flat_block_elems.restype = i32
     lib.psgd_flat_block_elems.argtypes = []
     lib.psgd_flat_launch.restype = i32
-    lib.psgd_flat_launch.argtypes = [i32, vp, vp, vp, i32, vp, vp, f32, vp, vp]
+    lib.psgd_flat_launch.argtypes = [i32, i32, vp, vp, vp, i32, vp, vp, f32, vp, C.c_longlong, vp]
 
     for name, sig in _OPTIONAL.items():
         fn = getattr(lib, name, None)
@@ -54,6 +54,10 @@ _OPTIONAL = {
     "psgd_topk_abs": (i32, [vp, i64, i64, vp, vp, vp, vp, vp]),
     "psgd_svd_tall_max_cols": (i32, []),
     "psgd_svd_tall_launch": (i32, [vp, i32, vp, vp, vp, vp, vp]),
+    "psgd_bulk_chunk_floats": (i64, []),
+    "psgd_bulk_arena_bytes": (i64, [i64, i32]),
+    "psgd_bulk_allreduce_launch": (i32, [vp, i64, i32, vp]),
+    "psgd_bulk_finish_launch": (i32, [vp, i64, i32, vp]),
     "psgd_symm_alloc": (i32, [C.c_size_t, C.POINTER(vp)]),
     "psgd_symm_free": (i32, [vp]),
     "psgd_symm_handle_bytes": (i32, []),

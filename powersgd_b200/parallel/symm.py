@@ -67,6 +67,21 @@ class SymmetricBuffer:
             self._imported.append(int(mapped.value))
         dist.barrier(group=group)
 
+    def tensor(self, offset_bytes: int, numel: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """A torch view of this rank's copy (no ownership: it must not outlive `close()`)."""
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        if offset_bytes % itemsize or offset_bytes + numel * itemsize > self.nbytes:
+            raise ValueError("view outside the symmetric buffer")
+        typestr = {torch.float32: "<f4", torch.int32: "<i4", torch.uint8: "|u1"}[dtype]
+
+        class _View:
+            __cuda_array_interface__ = {
+                "shape": (int(numel),), "typestr": typestr, "data": (self.local + int(offset_bytes), False),
+                "version": 2, "strides": None,
+            }
+
+        return torch.as_tensor(_View(), device=torch.device("cuda", torch.cuda.current_device()))
+
     def close(self) -> None:
         if self.local == 0:
             return

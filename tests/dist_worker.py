@@ -64,6 +64,83 @@ def scenario_channel_allreduce():
         print("SCENARIO-OK")
 
 
+def scenario_flat_twoshot():
+    """Large uncompressed buffers take the two-shot (reduce-scatter + all-gather) peer-store path,
+    plain floats with one flag per chunk. Compare it with the library all-reduce, with and
+    without the fused SGD update, for 16-byte aligned tensors and for odd views."""
+    rank, world, dev = _init("nccl")
+    from powersgd_b200.cuda_path import NativeCompressor, NativeFlatAllReduce, _to_device
+
+    shapes = [(1000, 333), (7,), (513, 1025), (3, 3, 3, 3)]  # odd total: the padded tail is exercised
+
+    def alloc(odd):
+        # odd: views that start one float into their storage, so the element-wise kernels run
+        if not odd:
+            return [torch.zeros(*s, device=dev) for s in shapes]
+        return [torch.zeros(1 + torch.Size(s).numel(), device=dev)[1:].view(*s) for s in shapes]
+
+    def fresh(step, grads, odd):
+        g = torch.Generator(device="cpu").manual_seed(1000 * step + rank)
+        if grads is None:
+            grads = alloc(odd)
+        for t in grads:
+            t.copy_(torch.randn(t.shape, generator=g))
+        return grads
+
+    def mean_of(grads):
+        out = [t.clone() for t in grads]
+        for t in out:
+            dist.all_reduce(t)
+            t.div_(world)
+        return out
+
+    for flavour, odd in (("aligned", False), ("odd", True)):
+        red, grads = NativeFlatAllReduce(), None
+        for step in range(4):
+            grads = fresh(step, grads, odd)
+            ref = mean_of(grads)
+            out = red.aggregate(grads)
+            torch.cuda.synchronize()
+            assert red.path == "bulk" and red.launches == 4 and red._vec == (0 if odd else 1), (red.path, red.launches)
+            red.comm.check()
+            for o, r_, t in zip(out, ref, grads):
+                assert _rel(o, r_) < 1e-6, (flavour, step, _rel(o, r_))
+                assert _same_on_all_ranks(o, world)
+                assert float(t.abs().max()) == 0.0  # inputs are zeroed like the reference's pack
+        # fused SGD on the consumer side
+        params = alloc(odd)
+        for p_ in params:
+            p_.copy_(torch.randn(p_.shape, device=dev))
+            dist.broadcast(p_, 0)
+        moms = alloc(odd)
+        expect = [p_.clone() for p_ in params]
+        hyper = NativeCompressor._default_hyper()
+        hyper["lr"], hyper["momentum"], hyper["has_momentum"], hyper["one_minus_dampening"] = 0.1, 0.9, 1, 1.0
+        hyper_dev = _to_device(hyper, dev)
+        red2, grads, ref_moms = NativeFlatAllReduce(), None, None
+        for step in range(3):
+            grads = fresh(50 + step, grads, odd)
+            mean = mean_of(grads)
+            red2.aggregate_and_step(grads, params, moms, [0] * len(grads), hyper_dev)
+            torch.cuda.synchronize()
+            red2.comm.check()
+            if ref_moms is None:
+                ref_moms = [gm.clone() for gm in mean]
+            else:
+                for rm, gm in zip(ref_moms, mean):
+                    rm.mul_(0.9).add_(gm)
+            for e, rm in zip(expect, ref_moms):
+                e.add_(rm, alpha=-0.1)
+            for p_, e in zip(params, expect):
+                assert _rel(p_, e) < 1e-5, (flavour, step, _rel(p_, e))
+                assert _same_on_all_ranks(p_, world)
+        dist.barrier()
+        red.comm.close()
+        red2.comm.close()
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
 def scenario_channel_timeout():
     """One rank stays away from a collective: the others' bounded waits give up, the kernels
     drain, the status word is set and the context stays usable."""
