@@ -45,6 +45,9 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--skip-reference", action="store_true")
     ap.add_argument("--only-ours", action="store_true", help="time only the native path (used for profiler captures)")
+    ap.add_argument("--flat-stages", action="store_true",
+                    help="multi-GPU: per-stage device times of the uncompressed peer-store all-reduce (pack, "
+                         "scatter + reduce, unpack) next to the library all-reduce, then exit")
     return ap.parse_args()
 
 
@@ -100,6 +103,58 @@ def time_aggregate(make_agg, grads, steps, warmup, flush, world, device):
     return ms, err, out
 
 
+def flat_stages(args, world, rank, device):
+    """Device time of each stage of NativeFlatAllReduce's two-shot path, max over ranks."""
+    import ctypes
+
+    from powersgd_b200.cuda_path import NativeFlatAllReduce, _stream_ptr
+    from powersgd_b200.ops import native
+
+    def timed(stages, before):
+        acc = [0.0] * len(stages)
+        for it in range(args.warmup + args.steps):
+            before()
+            dist.barrier()
+            torch.cuda.synchronize()
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(stages) + 1)]
+            evs[0].record()
+            for i, stage in enumerate(stages):
+                stage()
+                evs[i + 1].record()
+            torch.cuda.synchronize()
+            if it >= args.warmup:
+                for i in range(len(stages)):
+                    acc[i] += evs[i].elapsed_time(evs[i + 1]) / args.steps
+        t = torch.tensor(acc, device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t]
+
+    for shape in args.shapes.split(","):
+        n, m = (int(v) for v in shape.lower().split("x"))
+        grads = [torch.randn(n, m, device=device) for _ in range(args.batch)]
+        refill = lambda: [g.normal_() for g in grads]  # noqa: E731
+        red = NativeFlatAllReduce()
+        red._bind(grads)
+        row = {"shape": [n, m], "batch": args.batch, "n_gpus": world, "path": red.path, "mbytes": 4e-6 * n * m * args.batch}
+        if red.path == "bulk":
+            hyper = red._hyper_dev
+            middle = lambda: native.check(  # noqa: E731
+                red.lib.psgd_bulk_allreduce_launch(red.comm.ptr, ctypes.c_longlong(red.n_pad), world, _stream_ptr()), "bulk")
+            t = timed([lambda: red._launch(0, hyper, float(world)), middle, lambda: red._launch(12, hyper, 1.0)], refill)
+            red.comm.check()
+            row.update({"pack_ms": t[0], "scatter_reduce_ms": t[1], "unpack_ms": t[2], "whole_path_ms": sum(t)})
+        else:
+            t = timed([lambda: red.aggregate(grads)], refill)
+            row["whole_path_ms"] = t[0]
+        red.close()
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        row["library_allreduce_ms"] = timed([lambda: dist.all_reduce(flat)], lambda: None)[0]
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+        del grads, flat
+        torch.cuda.empty_cache()
+
+
 def main():
     args = parse()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -111,6 +166,13 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     from powersgd_b200 import BasicConfig, BasicPowerSGD
+
+    if args.flat_stages:
+        if world < 2:
+            raise SystemExit("--flat-stages needs at least two ranks")
+        flat_stages(args, world, rank, device)
+        dist.destroy_process_group()
+        return
 
     ref = None if (args.skip_reference or args.only_ours) else reference_module()
     peaks = {}

@@ -1,6 +1,7 @@
 #!/usr/bin/env python3
 """Collective micro-benchmark: all_reduce / all_gather / gather / broadcast at 14 message sizes
-(4 B ... 256 MiB), plus this library's in-kernel one-shot all-reduce beside NCCL's.
+(4 B ... 256 MiB), plus this library's in-kernel all-reduces beside NCCL's: the one-shot
+flag-in-data kernel up to 4 MiB and the two-shot bulk kernel above.
 
 Protocol of paper-code/timings.py:16-39, 65-115 (barrier before every repetition, `repetitions`
 samples per size, summary table and JSON). Timing differs on purpose: on CUDA every sample is a
@@ -112,6 +113,15 @@ def main():
             for _ in range(reps):
                 samples.time(f"in_kernel_all_reduce_{size}", lambda: channel.all_reduce_(data))
             channel.check()
+        elif channel is not None:
+            from ..parallel.symm import BulkAllReduce
+
+            bulk = BulkAllReduce(data.numel())
+            bulk.buffer.copy_(data)
+            for _ in range(reps):
+                samples.time(f"in_kernel_all_reduce_{size}", bulk.all_reduce_)
+            bulk.check()
+            bulk.close()
     for size in config["message_sizes"]:
         data = torch.randn(max(size // 4, 1), device=device)
         outs = [torch.empty_like(data) for _ in range(world)]

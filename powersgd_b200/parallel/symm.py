@@ -172,3 +172,41 @@ class Channel:
         if self._status_host:
             self.lib.psgd_status_free(self._status_host)
             self._status_host = None
+
+
+class BulkAllReduce:
+    """In-place SUM all-reduce of a large float32 buffer that lives in symmetric memory.
+
+    Two-shot over peer stores with plain floats and one epoch flag per 16 KiB chunk
+    (csrc/comm_kernels.cu): every rank pushes the slices it does not own to their owners, owners
+    add the W contributions in rank order and store the sum into everybody's buffer. Three
+    launches, no library collective, recordable in a CUDA graph. Fill `buffer` (a view of this
+    rank's arena), call `all_reduce_()`, read `buffer`. The reference uses NCCL's all-reduce for
+    this (powersgd/powersgd.py:22-31, paper-code/gradient_reducers.py ExactReducer).
+    """
+
+    def __init__(self, numel: int, group=None, timeout_ms: Optional[float] = None):
+        lib = native.lib()
+        world = dist.get_world_size(group)
+        unit = world * int(lib.psgd_bulk_chunk_floats())
+        self.numel = int(numel)
+        self.n_pad = -(-self.numel // unit) * unit
+        nbytes = int(lib.psgd_bulk_arena_bytes(ctypes.c_longlong(self.n_pad), world))
+        self.channel = Channel(-(-nbytes // (16 * world)), group, timeout_ms)
+        self.world = world
+        self.buffer = self.channel.slots.tensor(0, self.n_pad)[: self.numel]
+
+    def all_reduce_(self) -> torch.Tensor:
+        ch = self.channel
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        native.check(ch.lib.psgd_bulk_allreduce_launch(ch.ptr, ctypes.c_longlong(self.n_pad), self.world, stream), "psgd_bulk_allreduce_launch")
+        native.check(ch.lib.psgd_bulk_finish_launch(ch.ptr, ctypes.c_longlong(self.n_pad), self.world, stream), "psgd_bulk_finish_launch")
+        return self.buffer
+
+    def check(self) -> None:
+        self.channel.check()
+
+    def close(self) -> None:
+        self.buffer = None
+        self.channel.close()
+

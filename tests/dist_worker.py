@@ -60,6 +60,24 @@ def scenario_channel_allreduce():
     assert torch.allclose(x, torch.full_like(x, expect), rtol=1e-5), x[:4]
     dist.barrier()
     ch.close()
+    # large messages: the two-shot kernel on a buffer in symmetric memory, several epochs in a row
+    from powersgd_b200.parallel.symm import BulkAllReduce
+
+    for n in (5, 3 * 4096 * world + 17, 1 << 21):
+        bulk = BulkAllReduce(n, timeout_ms=5000)
+        for it in range(3):
+            g = torch.Generator(device="cpu").manual_seed(7 * it + rank + n)
+            x = torch.randn(n, generator=g).to(dev)
+            ref = x.clone()
+            dist.all_reduce(ref)
+            bulk.buffer.copy_(x)
+            out = bulk.all_reduce_()
+            torch.cuda.synchronize()
+            bulk.check()
+            assert _rel(out, ref) < 1e-6, (n, it, _rel(out, ref))
+            assert _same_on_all_ranks(out, world)
+        dist.barrier()
+        bulk.close()
     if rank == 0:
         print("SCENARIO-OK")
 
