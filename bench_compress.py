@@ -45,6 +45,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--skip-reference", action="store_true")
     ap.add_argument("--only-ours", action="store_true", help="time only the native path (used for profiler captures)")
+    ap.add_argument("--stages", action="store_true", help="add per-phase device times of the native path to every row")
     ap.add_argument("--flat-stages", action="store_true",
                     help="multi-GPU: per-stage device times of the uncompressed peer-store all-reduce (pack, "
                          "scatter + reduce, unpack) next to the library all-reduce, then exit")
@@ -71,12 +72,18 @@ def reference_module():
     return None
 
 
-def time_aggregate(make_agg, grads, steps, warmup, flush, world, device):
+def time_aggregate(make_agg, grads, steps, warmup, flush, world, device, stages=None):
+    """`stages`: a dict that receives the mean device time of every named phase of the native
+    path (CUDA-event pairs between its launches), max over ranks."""
+    from powersgd_b200.cuda_path import _Range
+
     agg = make_agg()
     work = [g.clone() for g in grads]
     times = []
     out = None
+    phase = {}
     for i in range(warmup + steps):
+        _Range.events = [] if (stages is not None and i >= warmup) else None
         for w, g in zip(work, grads):
             w.copy_(g)  # same input every iteration: the timing does not depend on the residual
         if flush is not None:
@@ -91,6 +98,15 @@ def time_aggregate(make_agg, grads, steps, warmup, flush, world, device):
         torch.cuda.synchronize()
         if i >= warmup:
             times.append(a.elapsed_time(b))
+            for name, ea, eb in _Range.events or []:
+                phase[name] = phase.get(name, 0.0) + ea.elapsed_time(eb) / steps
+    _Range.events = None
+    if stages is not None and phase:
+        names = sorted(phase)
+        t = torch.tensor([phase[k] for k in names], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        stages.update({k: round(float(v), 5) for k, v in zip(names, t)})
     ms = sum(times) / len(times)
     if world > 1:
         t = torch.tensor([ms], device=device, dtype=torch.float64)
@@ -192,14 +208,18 @@ def main():
         for r in (int(v) for v in args.ranks.split(",")):
             for iters in (int(v) for v in args.iters.split(",")):
                 cfg = BasicConfig(rank=r, num_iters_per_step=iters)
+                stages = {} if args.stages else None
                 ours_ms, ours_err, _ = time_aggregate(
-                    lambda: BasicPowerSGD(grads, cfg, backend="native"), grads, args.steps, args.warmup, flush, world, device
+                    lambda: BasicPowerSGD(grads, cfg, backend="native"), grads, args.steps, args.warmup, flush, world, device,
+                    stages=stages,
                 )
                 row = {
                     "shape": [n, m], "batch": args.batch, "rank": r, "iters": iters, "n_gpus": world,
                     "ours_ms": ours_ms, "ours_rel_error": ours_err / norm_in,
                     "l2": "flush between iterations" if flush is not None else "inputs larger than L2",
                 }
+                if stages:
+                    row["ours_phase_ms"] = stages
                 # algorithmic traffic: `iters` reads of M, then read M + write residual + write update
                 traffic = (iters + 3) * nbytes
                 row["ours_gbs"] = traffic / (ours_ms * 1e-3) / 1e9

@@ -47,10 +47,16 @@ __device__ __forceinline__ float psgd_sgd_update(float g, float& p, float* mom_p
 
 // SAME: one worker, so the summed factors ARE the local ones and the update equals what is
 // removed from the gradient: one accumulator, half the shared-memory traffic and FMAs.
+// General kernel (any K): panels of FIN_KC factor columns are re-staged for every 32-row chunk.
 template <int VEC, bool SAME>
 __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs a) {
-  const PsgdTile t = a.tiles[blockIdx.x];
-  const PsgdMat mt = a.mats[t.mat];
+  const PsgdTile whole = a.tiles[blockIdx.x];
+  const PsgdMat mt = a.mats[whole.mat];
+  for (int rc = 0; rc < whole.rows; rc += FIN_ROWS) {
+  PsgdTile t = whole;
+  t.row0 = whole.row0 + rc;
+  t.rows = min(FIN_ROWS, whole.rows - rc);
+  __syncthreads();  // the previous chunk is done with the panels
   const int r = mt.r, m = mt.m;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = a.nhist * r;
@@ -189,13 +195,184 @@ __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs
       }
     }
   }
+  }  // row chunks
 }
 
-PSGD_API int psgd_finalize_launch(int vec4, const void* mats, const void* tiles, int ntiles, const void* hyper,
-                                  int nhist, const float* const* lloc, const float* const* rloc,
+// Strip kernel (K = half-iterations x rank <= FIN_STRIP_KMAX): a CTA owns a strip of up to
+// `tile_rows` rows x 128 columns. All factor panels of the strip are staged in shared memory
+// once; the loop over 32-row chunks then runs without barriers, every chunk issuing its global
+// loads (gradient, parameter, momentum) before its FMA loop so that their latency overlaps it.
+constexpr int FIN_STRIP_KMAX = 32;
+
+template <int VEC, bool SAME>
+__global__ void __launch_bounds__(FIN_THREADS, 2) psgd_finalize_strip_kernel(FinalizeArgs a, int tile_rows) {
+  extern __shared__ __align__(16) float fin_smem[];
+  const PsgdTile t = a.tiles[blockIdx.x];
+  const PsgdMat mt = a.mats[t.mat];
+  const int r = mt.r, m = mt.m;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int K = a.nhist * r;
+  float* sRl = fin_smem;                         // [K][FIN_COLS]
+  float* sLl = sRl + K * FIN_COLS;               // [K][tile_rows]
+  float* sRs = SAME ? sRl : sLl + K * tile_rows;
+  float* sLs = SAME ? sLl : sRs + K * FIN_COLS;
+
+  for (int h = 0; h < a.nhist; ++h) {
+    {
+      const long long base = mt.q_off + (long long)t.col0 * r;
+      const float* gl = a.rloc[h] + base;
+      const float* gs = a.rsum[h] + base;
+      for (int e = tid; e < t.cols * r; e += FIN_THREADS) {
+        const int lc = e / r, j = e - lc * r;
+        // lane-major placement so that each lane's 4 columns are adjacent for the strided layout
+        const int pos = (VEC == 4) ? lc : ((lc & 31) * 4 + (lc >> 5));
+        sRl[(h * r + j) * FIN_COLS + pos] = gl[e];
+        if (!SAME) sRs[(h * r + j) * FIN_COLS + pos] = gs[e];
+      }
+    }
+    {
+      const long long base = mt.p_off + (long long)t.row0 * r;
+      const float* gl = a.lloc[h] + base;
+      const float* gs = a.lsum[h] + base;
+      for (int e = tid; e < t.rows * r; e += FIN_THREADS) {
+        const int lr = e / r, j = e - lr * r;
+        sLl[(h * r + j) * tile_rows + lr] = gl[e];
+        if (!SAME) sLs[(h * r + j) * tile_rows + lr] = gs[e];
+      }
+    }
+  }
+  __syncthreads();
+  const PsgdHyper hy = a.hyper[mt.hyper];
+  const bool sgd = a.fused_sgd != 0;
+  const bool mom = sgd && hy.has_momentum;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  for (int rc = 0; rc < t.rows; rc += FIN_ROWS) {
+    // ---- global loads of this chunk first ----
+    float4 g4[4], p4[4], m4[4];
+    bool live[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int lr = rc + warp * 4 + u;
+      const long long rowoff = (long long)(t.row0 + lr) * m + t.col0;
+      g4[u] = p4[u] = m4[u] = zero4;
+      if (VEC == 4) {
+        live[u] = lr < t.rows && lane * 4 < t.cols;
+        if (live[u]) {
+          g4[u] = *reinterpret_cast<const float4*>(mt.grad + rowoff + lane * 4);
+          if (sgd) p4[u] = *reinterpret_cast<const float4*>(mt.param + rowoff + lane * 4);
+          if (mom) m4[u] = *reinterpret_cast<const float4*>(mt.mom + rowoff + lane * 4);
+        }
+      } else {
+        live[u] = lr < t.rows;
+        if (live[u]) {
+          float* gv = reinterpret_cast<float*>(&g4[u]);
+          float* pv = reinterpret_cast<float*>(&p4[u]);
+          float* mv = reinterpret_cast<float*>(&m4[u]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int lc = lane + 32 * c;
+            if (lc < t.cols) {
+              gv[c] = mt.grad[rowoff + lc];
+              if (sgd) pv[c] = mt.param[rowoff + lc];
+              if (mom) mv[c] = mt.mom[rowoff + lc];
+            }
+          }
+        }
+      }
+    }
+    // ---- rank-K update from the staged panels ----
+    float accE[4][4], accA[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) accE[u][c] = accA[u][c] = 0.f;
+#pragma unroll 4
+    for (int k = 0; k < K; ++k) {
+      const float4 ll = *reinterpret_cast<const float4*>(sLl + k * tile_rows + rc + warp * 4);
+      const float4 rl = *reinterpret_cast<const float4*>(sRl + k * FIN_COLS + lane * 4);
+      const float4 ls = SAME ? ll : *reinterpret_cast<const float4*>(sLs + k * tile_rows + rc + warp * 4);
+      const float4 rs = SAME ? rl : *reinterpret_cast<const float4*>(sRs + k * FIN_COLS + lane * 4);
+      const float lv[4] = {ll.x, ll.y, ll.z, ll.w}, sv[4] = {ls.x, ls.y, ls.z, ls.w};
+      const float rlv[4] = {rl.x, rl.y, rl.z, rl.w}, rsv[4] = {rs.x, rs.y, rs.z, rs.w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          accE[u][c] = fmaf(lv[u], rlv[c], accE[u][c]);
+          if (!SAME) accA[u][c] = fmaf(sv[u], rsv[c], accA[u][c]);
+        }
+    }
+    // ---- residual, mean update, optimizer ----
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (!live[u]) continue;
+      const int lr = rc + warp * 4 + u;
+      const long long rowoff = (long long)(t.row0 + lr) * m + t.col0;
+      float* gv = reinterpret_cast<float*>(&g4[u]);
+      float* pv = reinterpret_cast<float*>(&p4[u]);
+      float* mv = reinterpret_cast<float*>(&m4[u]);
+      float av[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        gv[c] -= accE[u][c];
+        av[c] = (SAME ? accE[u][c] : accA[u][c]) * a.inv_world;
+        if (sgd) psgd_sgd_update(av[c], pv[c], &mv[c], hy);
+      }
+      if (VEC == 4) {
+        *reinterpret_cast<float4*>(mt.grad + rowoff + lane * 4) = g4[u];
+        if (sgd) {
+          *reinterpret_cast<float4*>(mt.param + rowoff + lane * 4) = p4[u];
+          if (mom) *reinterpret_cast<float4*>(mt.mom + rowoff + lane * 4) = m4[u];
+        } else {
+          *reinterpret_cast<float4*>(mt.out + rowoff + lane * 4) = make_float4(av[0], av[1], av[2], av[3]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int lc = lane + 32 * c;
+          if (lc >= t.cols) continue;
+          mt.grad[rowoff + lc] = gv[c];
+          if (sgd) {
+            mt.param[rowoff + lc] = pv[c];
+            if (mom) mt.mom[rowoff + lc] = mv[c];
+          } else {
+            mt.out[rowoff + lc] = av[c];
+          }
+        }
+      }
+    }
+  }
+}
+
+template <int VEC, bool SAME>
+static int finalize_strip_launch(const FinalizeArgs& a, int ntiles, int tile_rows, int kmax, cudaStream_t stream) {
+  const size_t smem = (size_t)(SAME ? 1 : 2) * kmax * (FIN_COLS + tile_rows) * sizeof(float);
+  psgd_finalize_strip_kernel<VEC, SAME><<<ntiles, FIN_THREADS, smem, stream>>>(a, tile_rows);
+  return 0;
+}
+
+// Tallest strip (multiple of 32 rows, at most 256) whose panels fit the shared-memory budget.
+PSGD_API int psgd_finalize_strip_rows(int kmax, int same) {
+  if (kmax > FIN_STRIP_KMAX) return FIN_ROWS;  // general kernel: strips only save tile overhead
+  const int budget = 48 * 1024;                // no opt-in needed, several CTAs per SM stay resident
+  int rows = budget / ((same ? 1 : 2) * kmax * (int)sizeof(float)) - FIN_COLS;
+  rows = rows / FIN_ROWS * FIN_ROWS;
+  return rows > 256 ? 256 : (rows < FIN_ROWS ? FIN_ROWS : rows);
+}
+
+// tile_rows: height of the tallest tile in `tiles` (a multiple of 32); max_r: largest rank of a
+// matrix in `mats`. With nhist * max_r <= 32 and panels that fit shared memory the strip kernel
+// runs, else the general one.
+PSGD_API int psgd_finalize_launch(int vec4, const void* mats, const void* tiles, int ntiles, int tile_rows, int max_r,
+                                  const void* hyper, int nhist, const float* const* lloc, const float* const* rloc,
                                   const float* const* lsum, const float* const* rsum, float inv_world,
                                   int fused_sgd, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
+  if (tile_rows <= 0 || tile_rows % FIN_ROWS != 0 || max_r <= 0) {
+    psgd_set_error("psgd_finalize_launch: tile_rows=%d must be a positive multiple of %d, max_r=%d positive", tile_rows, FIN_ROWS, max_r);
+    return -1;
+  }
   if (nhist > PSGD_MAX_HIST) {
     psgd_set_error("psgd_finalize_launch: %d half-iterations beyond the compiled maximum", nhist);
     return -1;
@@ -215,6 +392,19 @@ PSGD_API int psgd_finalize_launch(int vec4, const void* mats, const void* tiles,
   a.fused_sgd = fused_sgd;
   bool same = true;
   for (int i = 0; i < nhist; ++i) same = same && lloc[i] == lsum[i] && rloc[i] == rsum[i];
+  const int kmax = nhist * max_r;
+  const size_t strip_smem = (size_t)(same ? 1 : 2) * kmax * (FIN_COLS + tile_rows) * sizeof(float);
+  if (kmax <= FIN_STRIP_KMAX && strip_smem <= 48 * 1024) {
+    if (vec4) {
+      if (same) { if (finalize_strip_launch<4, true>(a, ntiles, tile_rows, kmax, stream)) return -1; }
+      else { if (finalize_strip_launch<4, false>(a, ntiles, tile_rows, kmax, stream)) return -1; }
+    } else {
+      if (same) { if (finalize_strip_launch<1, true>(a, ntiles, tile_rows, kmax, stream)) return -1; }
+      else { if (finalize_strip_launch<1, false>(a, ntiles, tile_rows, kmax, stream)) return -1; }
+    }
+    PSGD_CUDA_OK(cudaGetLastError());
+    return 0;
+  }
   if (vec4) {
     if (same) psgd_finalize_kernel<4, true><<<ntiles, FIN_THREADS, 0, stream>>>(a);
     else psgd_finalize_kernel<4, false><<<ntiles, FIN_THREADS, 0, stream>>>(a);

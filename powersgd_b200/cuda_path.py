@@ -33,9 +33,12 @@ from .utils import is_distributed, world_size
 
 
 class _Range:
-    """NVTX range when PSGD_B200_NVTX=1 (phase names show up in Nsight timelines); free otherwise."""
+    """A named phase of `aggregate()`: an NVTX range when PSGD_B200_NVTX=1 (phase names show up
+    in profiler timelines), a CUDA-event pair appended to `_Range.events` when a benchmark set
+    that list (per-phase device times), free otherwise."""
 
     enabled = os.environ.get("PSGD_B200_NVTX", "0") == "1"
+    events: Optional[list] = None
 
     def __init__(self, name: str):
         self.name = name
@@ -43,8 +46,15 @@ class _Range:
     def __enter__(self):
         if self.enabled:
             torch.cuda.nvtx.range_push(self.name)
+        if _Range.events is not None:
+            self._start = torch.cuda.Event(enable_timing=True)
+            self._start.record()
 
     def __exit__(self, *exc):
+        if _Range.events is not None:
+            stop = torch.cuda.Event(enable_timing=True)
+            stop.record()
+            _Range.events.append((self.name, self._start, stop))
         if self.enabled:
             torch.cuda.nvtx.range_pop()
 
@@ -119,6 +129,7 @@ class TilePlan:
         self.nn_cols_cap = 1024
         self.rp_tc = lib.psgd_gemm_tc_rank_pad(self.max_r)
         self.fin_tc_ok = False  # set by the compressor: (half-iterations x rank) fits the tensor-core finalize
+        self.fin_rows = 32      # set by the compressor: height of a finalize strip (multiple of 32)
 
     def build(self, vec_flags: Sequence[bool], tc_flags: Optional[Sequence[bool]] = None):
         """Tile arrays split by vector width (CUDA-core kernels: keys 4 and 1) and, for the
@@ -141,9 +152,9 @@ class TilePlan:
                     for c0 in range(0, g.m, 64):
                         fin["tc"].append((mi, r0, min(128, g.n - r0), c0, min(64, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
             else:
-                for r0 in range(0, g.n, 32):
+                for r0 in range(0, g.n, self.fin_rows):
                     for c0 in range(0, g.m, 128):
-                        fin[v].append((mi, r0, min(32, g.n - r0), c0, min(128, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
+                        fin[v].append((mi, r0, min(self.fin_rows, g.n - r0), c0, min(128, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
             if tc_flags[mi]:
                 row_blocks = _split_even(g.n, tc_k, 32)
                 for c0 in range(0, g.m, 128):
@@ -216,6 +227,11 @@ class NativeCompressor:
         )
         if self.T > layout.MAX_HIST:
             raise ValueError(f"num_iters_per_step {self.T} exceeds the compiled maximum {layout.MAX_HIST}")
+        # finalize strips: as tall as the factor panels allow in shared memory, but short enough
+        # that a small model still spreads over ~6 strips per SM
+        strip_cap = int(self.lib.psgd_finalize_strip_rows(self.T * self.tiles.max_r, 1 if world_size() == 1 else 0))
+        want = self.tiles.total_elems // (128 * 148 * 6)
+        self.tiles.fin_rows = max(32, min(strip_cap, want // 32 * 32))
         nm = len(self.tiles.mats)
         cap = max(self.plan.p_total, self.plan.q_total, 1)
         f32 = dict(device=self.device, dtype=torch.float32)
@@ -434,6 +450,8 @@ class NativeCompressor:
                 _ptr(self._mats_dev),
                 _ptr(tiles),
                 count,
+                self.tiles.fin_rows,
+                self.tiles.max_r,
                 _ptr(self._hyper_dev),
                 len(sides),
                 ctypes.cast(_ptr_array(lloc), ctypes.c_void_p),
@@ -477,18 +495,19 @@ class NativeCompressor:
             with _Range(f"psgd.iter{t}.product"):
                 self._gemm(left, self.h_in[t], self.h_loc[t], other, self.cmat[t])
             total = state_out.numel()
-            if workers > 1 and self.comm is not None:
-                code = self.lib.psgd_factor_reduce_launch(
-                    self.comm.ptr, ctypes.c_longlong(total), _ptr(self.h_sum[t]), _ptr(state_out), _stream_ptr()
-                )
-                native.check(code, "psgd_factor_reduce_launch")
-                self.launches += 1
-            elif workers > 1:
-                self.h_sum[t][:total].copy_(self.h_loc[t][:total])
-                self._allreduce_sum(self.h_sum[t][:total])
-                state_out.copy_(self.h_sum[t][:total])
-            else:
-                state_out.copy_(self.h_loc[t][:total])
+            with _Range(f"psgd.iter{t}.reduce"):
+                if workers > 1 and self.comm is not None:
+                    code = self.lib.psgd_factor_reduce_launch(
+                        self.comm.ptr, ctypes.c_longlong(total), _ptr(self.h_sum[t]), _ptr(state_out), _stream_ptr()
+                    )
+                    native.check(code, "psgd_factor_reduce_launch")
+                    self.launches += 1
+                elif workers > 1:
+                    self.h_sum[t][:total].copy_(self.h_loc[t][:total])
+                    self._allreduce_sum(self.h_sum[t][:total])
+                    state_out.copy_(self.h_sum[t][:total])
+                else:
+                    state_out.copy_(self.h_loc[t][:total])
         return sides
 
     def _allreduce_sum(self, flat: torch.Tensor) -> None:

@@ -26,7 +26,7 @@ def declare(lib) -> None:
     lib.psgd_gemm_ffma_launch.argtypes = [i32, i32, i32, vp, vp, i32, vp, vp, i32, vp, vp, vp, vp, vp, vp]
 
     lib.psgd_finalize_launch.restype = i32
-    lib.psgd_finalize_launch.argtypes = [i32, vp, vp, i32, vp, i32, vp, vp, vp, vp, f32, i32, vp]
+    lib.psgd_finalize_launch.argtypes = [i32, vp, vp, i32, i32, i32, vp, i32, vp, vp, vp, vp, f32, i32, vp]
 
     lib.psgd_flat_block_elems.restype = i32
     lib.psgd_flat_block_elems.argtypes = []
@@ -48,6 +48,7 @@ _OPTIONAL = {
     "psgd_gemm_tc_rank_pad": (i32, [i32]),
     "psgd_tma_encode_matrix": (i32, [vp, vp, i32, i32]),
     "psgd_gemm_tc_launch": (i32, [i32, i32, i32, vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp]),
+    "psgd_finalize_strip_rows": (i32, [i32, i32]),
     "psgd_finalize_tc_max_k": (i32, []),
     "psgd_finalize_tc_launch": (i32, [vp, vp, i32, vp, vp, i32, i32, vp, vp, vp, vp, f32, i32, vp, vp]),
     "psgd_topk_workspace_ints": (i32, []),
