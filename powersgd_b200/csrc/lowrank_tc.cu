@@ -37,7 +37,9 @@ constexpr int TC_THREADS = 192;
 constexpr int TC_BK = 32;           // K elements (floats) per stage
 constexpr int TC_TILE = 128;        // output rows of the accumulator (UMMA M)
 constexpr int TC_A_BYTES = TC_TILE * TC_BK * 4;   // 16 KiB
-constexpr int TC_STAGES = 3;
+constexpr int TC_STAGES = 4;      // landing ring of the gradient tile (TMA -> shared memory)
+constexpr int TC_OP_STAGES = 2;   // ring of the operands the converters write (A_lo, factor slab):
+                                  // shallower than the landing ring, two CTAs still fit one SM
 constexpr uint64_t TC_WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 struct TcArgs {
@@ -172,9 +174,11 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = base;                                            // [STAGES][16 KiB]
-  uint8_t* sAlo = sA + TC_STAGES * TC_A_BYTES;                   // [STAGES][16 KiB] (SPLIT only)
-  uint8_t* sB = sAlo + (SPLIT ? TC_STAGES * TC_A_BYTES : 0);     // [STAGES][B_BYTES]
-  __shared__ __align__(8) uint64_t bar_full[TC_STAGES], bar_ready[TC_STAGES], bar_empty[TC_STAGES], bar_accum;
+  uint8_t* sAlo = sA + TC_STAGES * TC_A_BYTES;                   // [OP_STAGES][16 KiB] (SPLIT only)
+  uint8_t* sB = sAlo + (SPLIT ? TC_OP_STAGES * TC_A_BYTES : 0);  // [OP_STAGES][B_BYTES]
+  // full: tile landed (TMA -> converters); ready: A_lo and factor slab written (converters -> MMA);
+  // empty: landing slot consumed (MMA -> TMA); op_empty: operand slot consumed (MMA -> converters)
+  __shared__ __align__(8) uint64_t bar_full[TC_STAGES], bar_empty[TC_STAGES], bar_ready[TC_OP_STAGES], bar_op_empty[TC_OP_STAGES], bar_accum;
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort, s_last;
 
@@ -189,8 +193,11 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
   if (tid == 0) {
     for (int s = 0; s < TC_STAGES; ++s) {
       mbar_init(&bar_full[s], 1);
-      mbar_init(&bar_ready[s], 128);
       mbar_init(&bar_empty[s], 1);
+    }
+    for (int s = 0; s < TC_OP_STAGES; ++s) {
+      mbar_init(&bar_ready[s], 128);
+      mbar_init(&bar_op_empty[s], 1);
     }
     mbar_init(&bar_accum, 1);
     s_abort = 0;
@@ -230,14 +237,13 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
     if (lane == 0) {
       bool ok = true;
       for (int kb = 0; kb < nk && ok; ++kb) {
-        const int s = kb % TC_STAGES;
-        const uint32_t ph = (kb / TC_STAGES) & 1;
-        ok = mbar_wait(&bar_ready[s], ph, abort_flag, a.status);
+        const int s = kb % TC_STAGES, so = kb % TC_OP_STAGES;
+        ok = mbar_wait(&bar_ready[so], (kb / TC_OP_STAGES) & 1, abort_flag, a.status);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t aaddr = smem_u32(sA + s * TC_A_BYTES);
-        const uint32_t laddr = smem_u32(sAlo + s * TC_A_BYTES);
-        const uint32_t baddr = smem_u32(sB + s * B_BYTES);
+        const uint32_t laddr = smem_u32(sAlo + so * TC_A_BYTES);
+        const uint32_t baddr = smem_u32(sB + so * B_BYTES);
 #pragma unroll
         for (int ks = 0; ks < TC_BK / 8; ++ks) {
           // NT (MN-major A): a slab holds 32 K rows of 128 bytes (32 columns); 8 K rows = two
@@ -251,7 +257,8 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
             umma_tf32(tmem, dl, db, IDESC, 1u);
           }
         }
-        umma_commit(&bar_empty[s]);   // frees the stage once these MMAs have read it
+        umma_commit(&bar_empty[s]);      // frees the landing slot once these MMAs have read it
+        umma_commit(&bar_op_empty[so]);  // and the operand slot
       }
       umma_commit(&bar_accum);        // accumulator complete (or abandoned)
     }
@@ -275,16 +282,17 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
     };
     fetch(0);
     for (int kb = 0; kb < nk; ++kb) {
-      const int s = kb % TC_STAGES;
+      const int s = kb % TC_STAGES, so = kb % TC_OP_STAGES;
       const uint32_t ph = (kb / TC_STAGES) & 1;
       float cur[PER_THREAD];
 #pragma unroll
       for (int i = 0; i < PER_THREAD; ++i) cur[i] = pre[i];
       fetch(kb + 1);
       if (!mbar_wait(&bar_full[s], ph, abort_flag, a.status)) break;
+      if (!mbar_wait(&bar_op_empty[so], ((kb / TC_OP_STAGES) & 1) ^ 1, abort_flag, a.status)) break;
       if (SPLIT) {
         const float4* src = reinterpret_cast<const float4*>(sA + s * TC_A_BYTES);
-        float4* dst = reinterpret_cast<float4*>(sAlo + s * TC_A_BYTES);
+        float4* dst = reinterpret_cast<float4*>(sAlo + so * TC_A_BYTES);
 #pragma unroll
         for (int i = 0; i < TC_A_BYTES / 16 / 128; ++i) {
           const float4 v = src[tid + i * 128];
@@ -292,7 +300,7 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
         }
       }
       // factor slab: B[n][k] for k in this stage, K-major rows of 128 bytes with 128-byte swizzle
-      uint8_t* bt = sB + s * B_BYTES;
+      uint8_t* bt = sB + so * B_BYTES;
 #pragma unroll
       for (int i = 0; i < PER_THREAD; ++i) {
         const int e = tid + i * 128;
@@ -309,7 +317,7 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
           reinterpret_cast<float*>(bt + (SPLIT ? 2 : 1) * RP * 128)[e] = 0.f;
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(&bar_ready[s]);
+      mbar_arrive(&bar_ready[so]);
     }
   }
 
@@ -393,7 +401,7 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
 template <bool TRANSPOSED, int RP, bool SPLIT>
 int launch_tc(const TcArgs& a, int ntiles, cudaStream_t stream) {
   constexpr int N2 = ((SPLIT ? 2 : 1) * RP) < 16 ? 16 : ((SPLIT ? 2 : 1) * RP);
-  const size_t smem = 1024 + (size_t)TC_STAGES * (TC_A_BYTES * (SPLIT ? 2 : 1) + N2 * 128);
+  const size_t smem = 1024 + (size_t)TC_STAGES * TC_A_BYTES + (size_t)TC_OP_STAGES * ((SPLIT ? TC_A_BYTES : 0) + N2 * 128);
   static bool configured = false;
   if (!configured) {
     PSGD_CUDA_OK(cudaFuncSetAttribute(psgd_gemm_tc_kernel<TRANSPOSED, RP, SPLIT>,

@@ -1,4 +1,4 @@
-// Batched orthonormalisation of tall factor matrices (one CTA per unit).
+// Batched orthonormalisation of tall factor matrices, spread over the whole GPU.
 //
 // Replaces the reference's per-group `torch.linalg.qr` / joint-norm division
 // (powersgd/orthogonalization.py:4-8) and the research harness' column-serial Gram-Schmidt
@@ -18,8 +18,13 @@
 // Rank-1 units keep the reference's quirk: ONE Frobenius norm over the whole shape group
 // (all B matrices jointly), floored at 1e-16, divides every entry.
 //
-// The same launch also produces the small cross products C_i = F_i^T X_hat against earlier
-// factors of the same side; the product kernels use them to deflate algebraically.
+// Two launches. The first cuts every unit into row chunks, one CTA each: partial Gram matrices
+// (and partial cross products F_i^T X against earlier factors of the same side) go to scratch;
+// the CTA that arrives last at the unit's ticket adds the partials in chunk order, factorises,
+// and publishes R^-1 plus the cross products C_i = (F_i^T X) R^-1 = F_i^T X_hat that the product
+// kernels use to deflate algebraically. The second launch applies R^-1 to every row chunk. A long
+// factor (an embedding with 50 000 rows, rank 16) thus takes microseconds instead of the
+// hundreds that one CTA per unit needed.
 #include "psgd_common.cuh"
 
 typedef struct {
@@ -28,99 +33,150 @@ typedef struct {
   int32_t nsub;       // sub-matrices in the unit (> 1 only for rank-1 groups)
   int32_t r;          // columns
   int32_t first_mat;  // descriptor index of sub-matrix 0 (sub-matrices are consecutive)
-  int32_t pad[3];
+  int32_t chunk0;     // index of the unit's first chunk (chunks of a unit are consecutive)
+  int32_t nchunks;
+  int32_t pad;
 } PsgdOrthUnit;  // 32 bytes
+
+typedef struct {
+  int32_t unit;
+  int32_t sub;    // sub-matrix the chunk lies in (chunks never straddle sub-matrices)
+  int32_t row0;   // first row, counted from the start of the unit
+  int32_t rows;
+} PsgdOrthChunk;  // 16 bytes
 
 struct OrthArgs {
   const PsgdOrthUnit* units;
+  const PsgdOrthChunk* chunks;
   float* x;                          // factor buffer, orthonormalised in place
   float* copy_to;                    // optional second destination (same layout) or null
   int nprev;                         // earlier same-side factor buffers
   const float* prev[PSGD_MAX_HIST];  // each laid out like x
   float* cmat[PSGD_MAX_HIST];        // out: [mat][r*r] blocks with stride PSGD_CMAT_STRIDE
+  double* part;                      // scratch: [chunk][1 + nprev][RT*RT] partial sums
+  double* rinv;                      // scratch: [unit][RT*RT]  R^-1 (rank 1: [0] = the divisor)
+  int* dead;                         // scratch: [unit][RT]     column status (see sDead)
+  int* tickets;                      // [unit], zero between launches
 };
 
-constexpr int ORTH_THREADS = 512;
-constexpr int ORTH_WARPS = ORTH_THREADS / 32;
+constexpr int ORTH_THREADS = 256;
+constexpr int ORTH_CHUNK_FLOATS = 4096;  // rows per chunk = 4096 / RT (16 KiB of the factor)
 
-// Deterministic CTA-wide sum of per-thread rows acc[RT] that belong to column `j`
-// (thread layout: j = tid % RT, row lane = tid / RT). Result in sm[j*RT + k].
+// Sum over the rows of a chunk of a[row][j] * b[row][k] for every pair (j, k), in float64 and in
+// a fixed order: row groups stride through the chunk, then the groups are added in order.
+// Result: out[j * RT + k] (global scratch), written by the threads with tid < RT * RT.
 template <int RT>
-__device__ __forceinline__ void cta_reduce_rows(double (&acc)[RT], double* sm, int tid) {
-  const int lane = tid & 31, warp = tid >> 5;
+__device__ __forceinline__ void chunk_pairs(const float* sa, const float* sb, int rows, double* red, double* out, int tid) {
+  constexpr int NP = RT * RT;
+  constexpr int PP = NP > ORTH_THREADS ? NP / ORTH_THREADS : 1;     // pairs per thread
+  constexpr int NG = NP >= ORTH_THREADS ? 1 : ORTH_THREADS / NP;    // row groups
+  const int g = NP >= ORTH_THREADS ? 0 : tid / NP;
+  double acc[PP];
 #pragma unroll
-  for (int k = 0; k < RT; ++k) {
+  for (int q = 0; q < PP; ++q) acc[q] = 0.0;
+  const int p0 = NP >= ORTH_THREADS ? tid : tid % NP;
+#pragma unroll 4
+  for (int row = g; row < rows; row += NG) {
 #pragma unroll
-    for (int o = 16; o >= RT; o >>= 1) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], o);
+    for (int q = 0; q < PP; ++q) {
+      const int p = p0 + q * ORTH_THREADS;
+      acc[q] = fma((double)sa[row * RT + p / RT], (double)sb[row * RT + p % RT], acc[q]);
+    }
   }
-  for (int w = 0; w < ORTH_WARPS; ++w) {
-    if (warp == w && lane < RT) {
+  if (NG == 1) {
 #pragma unroll
-      for (int k = 0; k < RT; ++k) {
-        if (w == 0) sm[lane * RT + k] = acc[k];
-        else sm[lane * RT + k] += acc[k];
-      }
+    for (int q = 0; q < PP; ++q) out[p0 + q * ORTH_THREADS] = acc[q];
+  } else {
+    red[tid] = acc[0];
+    __syncthreads();
+    if (tid < NP) {
+      double s = 0.0;
+      for (int gg = 0; gg < NG; ++gg) s += red[gg * NP + tid];
+      out[tid] = s;
     }
     __syncthreads();
   }
 }
 
 template <int RT>
-__global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_kernel(OrthArgs a) {
-  const PsgdOrthUnit u = a.units[blockIdx.x];
+__global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_gram_kernel(OrthArgs a) {
+  constexpr int NP = RT * RT;
+  const PsgdOrthChunk ch = a.chunks[blockIdx.x];
+  const PsgdOrthUnit u = a.units[ch.unit];
   const int r = u.r;
   const int tid = threadIdx.x;
-  const long long len = (long long)u.sub_len * u.nsub;
-  float* __restrict__ x = a.x + u.x_off;
-  float* __restrict__ x2 = a.copy_to ? a.copy_to + u.x_off : nullptr;
+  const float* __restrict__ x = a.x + u.x_off;
 
-  __shared__ double sG[RT * RT];
-  __shared__ double sR[RT * RT];     // upper-triangular Cholesky factor, then its inverse
-  __shared__ double sRinv[RT * RT];
-  __shared__ int sDead[RT];          // -1: alive; >= 0: row of the substituted basis vector; -2: dropped
-  __shared__ float sScale;
+  __shared__ __align__(16) float sx[ORTH_CHUNK_FLOATS];
+  __shared__ __align__(16) float sf[ORTH_CHUNK_FLOATS];
+  __shared__ double red[ORTH_THREADS];
+  __shared__ double sG[NP];
+  __shared__ int sDead[RT];      // -1: alive; >= 0: row of the substituted basis vector; -2: dropped
+  __shared__ int s_last;
+  // used by the finishing CTA only, after the staging buffers are dead
+  static_assert(NP * sizeof(double) <= ORTH_CHUNK_FLOATS * sizeof(float), "R must fit a staging buffer");
+  double* sR = reinterpret_cast<double*>(sf);      // upper-triangular Cholesky factor
+  double* sRinv = reinterpret_cast<double*>(sx);
 
-  const int j = tid % RT;            // column owned by this thread in the Gram phases
-  const int rl = tid / RT;           // row lane
-  constexpr int NRL = ORTH_THREADS / RT;
-
-  // ---- Gram matrix -----------------------------------------------------------------------
-  {
-    double acc[RT];
-#pragma unroll
-    for (int k = 0; k < RT; ++k) acc[k] = 0.0;
-    if (j < r) {
-#pragma unroll 4
-      for (long long row = rl; row < len; row += NRL) {
-        const float* xr = x + row * r;
-        const double xj = (double)xr[j];
-#pragma unroll
-        for (int k = 0; k < RT; ++k)
-          if (k < r) acc[k] = fma(xj, (double)xr[k], acc[k]);
-      }
-    }
-    cta_reduce_rows<RT>(acc, sG, tid);
+  // ---- partial sums of this chunk ---------------------------------------------------------
+  const int stride = 1 + a.nprev;
+  double* my_part = a.part + (long long)blockIdx.x * stride * NP;
+  for (int e = tid; e < ch.rows * RT; e += ORTH_THREADS) {
+    const int row = e / RT, c = e % RT;
+    sx[e] = c < r ? x[(long long)(ch.row0 + row) * r + c] : 0.f;
   }
+  __syncthreads();
+  chunk_pairs<RT>(sx, sx, ch.rows, red, my_part, tid);
+  for (int p = 0; p < a.nprev; ++p) {
+    const float* __restrict__ f = a.prev[p] + u.x_off;
+    __syncthreads();
+    for (int e = tid; e < ch.rows * RT; e += ORTH_THREADS) {
+      const int row = e / RT, c = e % RT;
+      sf[e] = c < r ? f[(long long)(ch.row0 + row) * r + c] : 0.f;
+    }
+    __syncthreads();
+    chunk_pairs<RT>(sf, sx, ch.rows, red, my_part + (long long)(1 + p) * NP, tid);
+  }
+
+  // ---- the chunk that arrives last finishes the unit ----------------------------------------
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = (psgd_atom_add_acqrel_gpu(a.tickets + ch.unit, 1) == u.nchunks - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const double* unit_part = a.part + (long long)u.chunk0 * stride * NP;
+  if (tid < NP) {
+    double s = 0.0;
+    for (int c = 0; c < u.nchunks; ++c) s += __ldcg(unit_part + (long long)c * stride * NP + tid);
+    sG[tid] = s;
+  }
+  __syncthreads();
+  double* rinv_out = a.rinv + (long long)ch.unit * NP;
+  int* dead_out = a.dead + (long long)ch.unit * RT;
+  const long long len = (long long)u.sub_len * u.nsub;
 
   if (RT == 1 || r == 1) {
     // joint Frobenius norm of the whole unit, float32 semantics of the division
+    const float d = fmaxf((float)sqrt(sG[0]), 1e-16f);
     if (tid == 0) {
-      float nrm = (float)sqrt(sG[0]);
-      sScale = fmaxf(nrm, 1e-16f);
+      rinv_out[0] = (double)d;
+      dead_out[0] = -1;
     }
-    __syncthreads();
-    const float d = sScale;
-    for (long long i = tid; i < len; i += ORTH_THREADS) {
-      float v = x[i] / d;
-      x[i] = v;
-      if (x2) x2[i] = v;
+    // cross products per sub-matrix: (sum of f * x over the sub-matrix) / d
+    for (int e = tid; e < a.nprev * u.nsub; e += ORTH_THREADS) {
+      const int p = e / u.nsub, s = e % u.nsub;
+      double t = 0.0;
+      for (int c = 0; c < u.nchunks; ++c)
+        if (a.chunks[u.chunk0 + c].sub == s) t += __ldcg(unit_part + ((long long)c * stride + 1 + p) * NP);
+      a.cmat[p][(long long)(u.first_mat + s) * PSGD_CMAT_STRIDE] = (float)(t / (double)d);
     }
   } else {
     // ---- Cholesky (one warp) with canonical-vector substitution -------------------------
     if (tid < 32) {
       const int lane = tid;
       if (lane < RT) sDead[lane] = -1;
-      for (int e = lane; e < RT * RT; e += 32) { sR[e] = 0.0; sRinv[e] = 0.0; }
+      for (int e = lane; e < NP; e += 32) { sR[e] = 0.0; sRinv[e] = 0.0; }
       __syncwarp();
       for (int c = 0; c < r; ++c) {
         // pivot of column c
@@ -191,74 +247,122 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_kernel(OrthArgs a) {
       }
     }
     __syncthreads();
-
-    // ---- X <- X' R^-1 --------------------------------------------------------------------
-#pragma unroll 2
-    for (long long row = tid; row < len; row += ORTH_THREADS) {
-      float* xr = x + row * r;
-      double xin[RT];
-#pragma unroll
-      for (int k = 0; k < RT; ++k) {
-        double v = 0.0;
-        if (k < r) {
+    if (tid < NP) rinv_out[tid] = sRinv[tid];
+    if (tid < RT) dead_out[tid] = sDead[tid];
+    // ---- cross products: C_p = (F_p^T X') R^-1, X' = X with the substituted columns ----------
+    for (int p = 0; p < a.nprev; ++p) {
+      const float* __restrict__ f = a.prev[p] + u.x_off;
+      __syncthreads();
+      if (tid < NP) {
+        const int j = tid / RT, k = tid % RT;
+        double s = 0.0;
+        if (j < r && k < r) {
           const int d = sDead[k];
-          v = (d == -1) ? (double)xr[k] : ((d >= 0 && d == (int)row) ? 1.0 : 0.0);
+          if (d == -1) {
+            for (int c = 0; c < u.nchunks; ++c) s += __ldcg(unit_part + ((long long)c * stride + 1 + p) * NP + tid);
+          } else if (d >= 0) {
+            s = (double)f[(long long)d * r + j];  // column k of X' is the basis vector e_d
+          }
         }
-        xin[k] = v;
+        sG[tid] = s;
       }
-#pragma unroll
-      for (int c = 0; c < RT; ++c) {
-        if (c < r) {
+      __syncthreads();
+      if (tid < NP) {
+        const int j = tid / RT, k = tid % RT;
+        if (j < r && k < r) {
           double o = 0.0;
-#pragma unroll
-          for (int k = 0; k <= c; ++k) o = fma(xin[k], sRinv[k * RT + c], o);
-          const float of = (float)o;
-          xr[c] = of;
-          if (x2) x2[row * r + c] = of;
+          for (int l = 0; l <= k; ++l) o = fma(sG[j * RT + l], sRinv[l * RT + k], o);
+          a.cmat[p][(long long)u.first_mat * PSGD_CMAT_STRIDE + j * r + k] = (float)o;
         }
       }
     }
   }
+  if (tid == 0) a.tickets[ch.unit] = 0;  // ready for the next launch
+}
 
-  // ---- cross products against earlier same-side factors ---------------------------------
-  if (a.nprev > 0) {
-    __syncthreads();  // make this CTA's writes to x visible to all its threads
-    for (int p = 0; p < a.nprev; ++p) {
-      const float* __restrict__ f = a.prev[p] + u.x_off;
-      for (int s = 0; s < u.nsub; ++s) {
-        double acc[RT];
+// Second launch: X <- X' R^-1 (rank 1: X / d) on every row chunk, optionally mirrored to copy_to.
+template <int RT>
+__global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_apply_kernel(OrthArgs a) {
+  constexpr int NP = RT * RT;
+  const PsgdOrthChunk ch = a.chunks[blockIdx.x];
+  const PsgdOrthUnit u = a.units[ch.unit];
+  const int r = u.r;
+  const int tid = threadIdx.x;
+  float* __restrict__ x = a.x + u.x_off;
+  float* __restrict__ x2 = a.copy_to ? a.copy_to + u.x_off : nullptr;
+  __shared__ double sRinv[NP];
+  __shared__ int sDead[RT];
+  if (tid < NP) sRinv[tid] = a.rinv[(long long)ch.unit * NP + tid];
+  if (tid < RT) sDead[tid] = a.dead[(long long)ch.unit * RT + tid];
+  __syncthreads();
+
+  if (RT == 1 || r == 1) {
+    const float d = (float)sRinv[0];
+    for (int i = tid; i < ch.rows; i += ORTH_THREADS) {
+      const float v = x[ch.row0 + i] / d;
+      x[ch.row0 + i] = v;
+      if (x2) x2[ch.row0 + i] = v;
+    }
+    return;
+  }
+  for (int lr = tid; lr < ch.rows; lr += ORTH_THREADS) {
+    const long long row = ch.row0 + lr;
+    float* xr = x + row * r;
+    double xin[RT];
 #pragma unroll
-        for (int k = 0; k < RT; ++k) acc[k] = 0.0;
-        if (j < r) {
-          const long long lo = (long long)s * u.sub_len, hi = lo + u.sub_len;
-#pragma unroll 4
-          for (long long row = lo + rl; row < hi; row += NRL) {
-            const double fj = (double)f[row * r + j];
-            const float* xr = x + row * r;
+    for (int k = 0; k < RT; ++k) {
+      double v = 0.0;
+      if (k < r) {
+        const int d = sDead[k];
+        v = (d == -1) ? (double)xr[k] : ((d >= 0 && d == (int)row) ? 1.0 : 0.0);
+      }
+      xin[k] = v;
+    }
 #pragma unroll
-            for (int k = 0; k < RT; ++k)
-              if (k < r) acc[k] = fma(fj, (double)xr[k], acc[k]);
-          }
-        }
-        cta_reduce_rows<RT>(acc, sG, tid);
-        float* c_out = a.cmat[p] + (long long)(u.first_mat + s) * PSGD_CMAT_STRIDE;
-        for (int e = tid; e < r * r; e += ORTH_THREADS) c_out[e] = (float)sG[(e / r) * RT + (e % r)];
-        __syncthreads();
+    for (int c = 0; c < RT; ++c) {
+      if (c < r) {
+        double o = 0.0;
+#pragma unroll
+        for (int k = 0; k <= c; ++k) o = fma(xin[k], sRinv[k * RT + c], o);
+        const float of = (float)o;
+        xr[c] = of;
+        if (x2) x2[row * r + c] = of;
       }
     }
   }
 }
 
-// Launch one CTA per unit; all units of one call share the template rank RT >= max r.
-PSGD_API int psgd_orth_launch(const void* units, int nunits, int max_r, float* x, float* copy_to, int nprev,
-                              const float* const* prev, float* const* cmat, cudaStream_t stream) {
-  if (nunits <= 0) return 0;
+template <int RT>
+static void orth_launch_rt(const OrthArgs& a, int nchunks, cudaStream_t stream) {
+  psgd_orth_gram_kernel<RT><<<nchunks, ORTH_THREADS, 0, stream>>>(a);
+  psgd_orth_apply_kernel<RT><<<nchunks, ORTH_THREADS, 0, stream>>>(a);
+}
+
+// Template rank used for factors of rank max_r, and the rows of one chunk at that rank.
+PSGD_API int psgd_orth_template_rank(int max_r) {
+  return max_r <= 1 ? 1 : max_r <= 2 ? 2 : max_r <= 4 ? 4 : max_r <= 8 ? 8 : max_r <= 16 ? 16 : 32;
+}
+PSGD_API int psgd_orth_chunk_rows(int max_r) { return ORTH_CHUNK_FLOATS / psgd_orth_template_rank(max_r); }
+// Scratch per chunk (doubles) for `nprev` earlier factors; per unit: RT*RT doubles and RT ints.
+PSGD_API int psgd_orth_part_doubles(int max_r, int nprev) {
+  const int rt = psgd_orth_template_rank(max_r);
+  return (1 + nprev) * rt * rt;
+}
+
+// units / chunks: device tables; all units of one call share the template rank RT >= max r.
+// part: nchunks * psgd_orth_part_doubles(max_r, nprev) doubles; rinv: nunits * RT*RT doubles;
+// dead: nunits * RT ints; tickets: nunits ints, zero (the kernel leaves them zero).
+PSGD_API int psgd_orth_launch(const void* units, int nunits, const void* chunks, int nchunks, int max_r, float* x,
+                              float* copy_to, int nprev, const float* const* prev, float* const* cmat,
+                              double* part, double* rinv, int* dead, int* tickets, cudaStream_t stream) {
+  if (nunits <= 0 || nchunks <= 0) return 0;
   if (max_r > PSGD_MAX_RANK || nprev > PSGD_MAX_HIST) {
     psgd_set_error("psgd_orth_launch: rank %d or history %d beyond the compiled maximum", max_r, nprev);
     return -1;
   }
   OrthArgs a;
   a.units = (const PsgdOrthUnit*)units;
+  a.chunks = (const PsgdOrthChunk*)chunks;
   a.x = x;
   a.copy_to = copy_to;
   a.nprev = nprev;
@@ -266,12 +370,18 @@ PSGD_API int psgd_orth_launch(const void* units, int nunits, int max_r, float* x
     a.prev[i] = i < nprev ? prev[i] : nullptr;
     a.cmat[i] = i < nprev ? cmat[i] : nullptr;
   }
-  if (max_r <= 1) psgd_orth_kernel<1><<<nunits, ORTH_THREADS, 0, stream>>>(a);
-  else if (max_r <= 2) psgd_orth_kernel<2><<<nunits, ORTH_THREADS, 0, stream>>>(a);
-  else if (max_r <= 4) psgd_orth_kernel<4><<<nunits, ORTH_THREADS, 0, stream>>>(a);
-  else if (max_r <= 8) psgd_orth_kernel<8><<<nunits, ORTH_THREADS, 0, stream>>>(a);
-  else if (max_r <= 16) psgd_orth_kernel<16><<<nunits, ORTH_THREADS, 0, stream>>>(a);
-  else psgd_orth_kernel<32><<<nunits, ORTH_THREADS, 0, stream>>>(a);
+  a.part = part;
+  a.rinv = rinv;
+  a.dead = dead;
+  a.tickets = tickets;
+  switch (psgd_orth_template_rank(max_r)) {
+    case 1: orth_launch_rt<1>(a, nchunks, stream); break;
+    case 2: orth_launch_rt<2>(a, nchunks, stream); break;
+    case 4: orth_launch_rt<4>(a, nchunks, stream); break;
+    case 8: orth_launch_rt<8>(a, nchunks, stream); break;
+    case 16: orth_launch_rt<16>(a, nchunks, stream); break;
+    default: orth_launch_rt<32>(a, nchunks, stream); break;
+  }
   PSGD_CUDA_OK(cudaGetLastError());
   return 0;
 }

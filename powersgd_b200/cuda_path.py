@@ -3,7 +3,7 @@
 Per optimizer step the reference issues several hundred small PyTorch ops
 (powersgd/powersgd.py:146-235). Here a step is, for T half-iterations:
 
-    T x [ orthonormalise (1 launch) -> grouped product (1-2 launches; multi-GPU: its epilogue
+    T x [ orthonormalise (2 launches) -> grouped product (1-2 launches; multi-GPU: its epilogue
           pushes the fresh factor to every peer) -> sum of the peers' slots (1 small launch) ]
       ->  decompress + error feedback (+ SGD) (1-2 launches)
 
@@ -141,9 +141,12 @@ class TilePlan:
         nt_slots = nn_slots = tc_slots = 0
         tc_flags = tc_flags or [False] * len(self.mats)
         n_tc_elems = sum(self.plan.groups[gi].n * self.plan.groups[gi].m for (gi, _p, _i), f in zip(self.mats, tc_flags) if f)
-        # K extent of one tensor-core tile: long enough to amortise the pipeline ramp, short
-        # enough that a small model still fills the GPU
-        tc_k = 512 if n_tc_elems >= (16 << 20) else 256
+        # K extent of one tensor-core tile: long enough to amortise the pipeline ramp and the
+        # epilogue, short enough that a small model still fills the GPU, and such that the last
+        # wave of CTAs is nearly full (the block scheduler runs TC_CTAS_PER_SM per SM at a time)
+        tc_mats = [self.plan.groups[gi] for (gi, _p, _i), f in zip(self.mats, tc_flags) if f]
+        tc_k_nt = self._pick_tc_k(tc_mats, transposed=True)
+        tc_k_nn = self._pick_tc_k(tc_mats, transposed=False)
         for mi, (gi, _pos, _idx) in enumerate(self.mats):
             g = self.plan.groups[gi]
             v = 4 if vec_flags[mi] else 1
@@ -156,13 +159,13 @@ class TilePlan:
                     for c0 in range(0, g.m, 128):
                         fin[v].append((mi, r0, min(self.fin_rows, g.n - r0), c0, min(128, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
             if tc_flags[mi]:
-                row_blocks = _split_even(g.n, tc_k, 32)
+                row_blocks = _split_even(g.n, tc_k_nt, 32)
                 for c0 in range(0, g.m, 128):
                     for si, (r0, rows) in enumerate(row_blocks):
                         nt["tc"].append((mi, r0, rows, c0, min(128, g.m - c0), si, len(row_blocks), ticket, tc_slots, (0, 0, 0)))
                     ticket += 1
                     tc_slots += len(row_blocks)
-                col_blocks = _split_even(g.m, tc_k, 32)
+                col_blocks = _split_even(g.m, tc_k_nn, 32)
                 for r0 in range(0, g.n, 128):
                     for si, (c0, cols) in enumerate(col_blocks):
                         nn["tc"].append((mi, r0, min(128, g.n - r0), c0, cols, si, len(col_blocks), ticket, tc_slots, (0, 0, 0)))
@@ -196,19 +199,50 @@ class TilePlan:
             "fin": {k: arr(v) for k, v in fin.items()},
         }
 
-    def orth_units(self, side: str) -> np.ndarray:
-        units = []
+    TC_CTAS_PER_SM = 2
+    TC_TILE_OVERHEAD_ROWS = 96  # prologue + epilogue of a tile, in units of streamed K rows
+
+    def _pick_tc_k(self, groups, transposed: bool) -> int:
+        if not groups:
+            return 512
+        if os.environ.get("PSGD_B200_TC_K"):
+            return int(os.environ["PSGD_B200_TC_K"])  # tuning knob: fixed K extent (a multiple of 32)
+        slots = 148 * self.TC_CTAS_PER_SM
+        best, best_score = 512, -1.0
+        for k in range(256, 1024 + 1, 32):
+            tiles = 0
+            for g in groups:
+                k_len, out_len = (g.n, g.m) if transposed else (g.m, g.n)
+                tiles += -(-out_len // 128) * len(_split_even(k_len, k, 32))
+            waves = -(-tiles // slots)
+            score = tiles / (waves * slots) * k / (k + self.TC_TILE_OVERHEAD_ROWS)
+            if score > best_score + 1e-9:
+                best, best_score = k, score
+        return best
+
+    def orth_units(self, side: str, chunk_rows: int) -> Tuple[np.ndarray, np.ndarray]:
+        """Units (one per matrix; one per shape group at rank 1) and their row chunks of at most
+        `chunk_rows` rows, which never straddle the sub-matrices of a rank-1 unit."""
+        units, chunks = [], []
         mi = 0
+
+        def add(base, length, nsub, r, first_mat):
+            chunk0 = len(chunks)
+            for sub in range(nsub):
+                for r0 in range(0, length, chunk_rows):
+                    chunks.append((len(units), sub, sub * length + r0, min(chunk_rows, length - r0)))
+            units.append((base, length, nsub, r, first_mat, chunk0, len(chunks) - chunk0, 0))
+
         for g in self.plan.groups:
             length = g.n if side == "p" else g.m
             base = g.p_offset if side == "p" else g.q_offset
             if g.r == 1:
-                units.append((base, length, g.batch, 1, mi, (0, 0, 0)))
+                add(base, length, g.batch, 1, mi)
             else:
                 for b in range(g.batch):
-                    units.append((base + b * length * g.r, length, 1, g.r, mi + b, (0, 0, 0)))
+                    add(base + b * length * g.r, length, 1, g.r, mi + b)
             mi += g.batch
-        return np.array(units, dtype=layout.ORTH_UNIT_DTYPE)
+        return np.array(units, dtype=layout.ORTH_UNIT_DTYPE), np.array(chunks, dtype=layout.ORTH_CHUNK_DTYPE)
 
 
 class NativeCompressor:
@@ -239,8 +273,20 @@ class NativeCompressor:
         self.h_loc = [torch.zeros(cap, **f32) for _ in range(self.T)]
         self.h_sum = [torch.zeros(cap, **f32) for _ in range(self.T)]
         self.cmat = [[torch.zeros(nm * layout.CMAT_STRIDE, **f32) for _ in range(t)] for t in range(self.T)]
-        self.units = {s: _to_device(self.tiles.orth_units(s), self.device) for s in ("p", "q")}
-        self.n_units = {s: len(self.tiles.orth_units(s)) for s in ("p", "q")}
+        chunk_rows = int(self.lib.psgd_orth_chunk_rows(self.tiles.max_r))
+        rt = int(self.lib.psgd_orth_template_rank(self.tiles.max_r))
+        self.units, self.chunks, self.n_units, self.n_chunks = {}, {}, {}, {}
+        for s in ("p", "q"):
+            units, chunks = self.tiles.orth_units(s, chunk_rows)
+            self.units[s], self.chunks[s] = _to_device(units, self.device), _to_device(chunks, self.device)
+            self.n_units[s], self.n_chunks[s] = len(units), len(chunks)
+        # scratch of the orthonormalisation: partial sums per chunk, R^-1 / column status / ticket per unit
+        part_doubles = int(self.lib.psgd_orth_part_doubles(self.tiles.max_r, max(self.T - 1, 0)))
+        max_units = max(max(self.n_units.values()), 1)
+        self._orth_part = torch.zeros(max(max(self.n_chunks.values()), 1) * part_doubles, device=self.device, dtype=torch.float64)
+        self._orth_rinv = torch.zeros(max_units * rt * rt, device=self.device, dtype=torch.float64)
+        self._orth_dead = torch.zeros(max_units * rt, device=self.device, dtype=torch.int32)
+        self._orth_tickets = torch.zeros(max_units, device=self.device, dtype=torch.int32)
         self._key = None
         self._out_arena: Optional[torch.Tensor] = None
         self._hyper_dev = _to_device(self._default_hyper(), self.device)
@@ -351,16 +397,22 @@ class NativeCompressor:
         code = self.lib.psgd_orth_launch(
             _ptr(self.units[side]),
             self.n_units[side],
+            _ptr(self.chunks[side]),
+            self.n_chunks[side],
             self.tiles.max_r,
             _ptr(x),
             _ptr(copy_to),
             len(prev),
             ctypes.cast(_ptr_array(prev), ctypes.c_void_p),
             ctypes.cast(_ptr_array(cm), ctypes.c_void_p),
+            _ptr(self._orth_part),
+            _ptr(self._orth_rinv),
+            _ptr(self._orth_dead),
+            _ptr(self._orth_tickets),
             _stream_ptr(),
         )
         native.check(code, "psgd_orth_launch")
-        self.launches += 1
+        self.launches += 2  # Gram + factorisation, then the application of R^-1
 
     def _gemm(self, transposed: bool, fin: torch.Tensor, fout: torch.Tensor, corr_fac, corr_c):
         name = "nt" if transposed else "nn"

@@ -14,7 +14,7 @@ def declare(lib) -> None:
     lib.psgd_device_info.argtypes = [C.POINTER(i32)] * 4
 
     lib.psgd_orth_launch.restype = i32
-    lib.psgd_orth_launch.argtypes = [vp, i32, i32, vp, vp, i32, vp, vp, vp]
+    lib.psgd_orth_launch.argtypes = [vp, i32, vp, i32, i32, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp]
 
     lib.psgd_gemm_nn_tile_rows.restype = i32
     lib.psgd_gemm_nn_tile_rows.argtypes = [i32]
@@ -49,6 +49,9 @@ _OPTIONAL = {
     "psgd_tma_encode_matrix": (i32, [vp, vp, i32, i32]),
     "psgd_gemm_tc_launch": (i32, [i32, i32, i32, vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp]),
     "psgd_finalize_strip_rows": (i32, [i32, i32]),
+    "psgd_orth_template_rank": (i32, [i32]),
+    "psgd_orth_chunk_rows": (i32, [i32]),
+    "psgd_orth_part_doubles": (i32, [i32, i32]),
     "psgd_finalize_tc_max_k": (i32, []),
     "psgd_finalize_tc_launch": (i32, [vp, vp, i32, vp, vp, i32, i32, vp, vp, vp, vp, f32, i32, vp, vp]),
     "psgd_topk_workspace_ints": (i32, []),

@@ -80,7 +80,12 @@ ORTH_UNIT_DTYPE = np.dtype(
         ("nsub", "<i4"),
         ("r", "<i4"),
         ("first_mat", "<i4"),
-        ("pad", "<i4", (3,)),
+        ("chunk0", "<i4"),
+        ("nchunks", "<i4"),
+        ("pad", "<i4"),
     ]
 )
 assert ORTH_UNIT_DTYPE.itemsize == 32
+
+ORTH_CHUNK_DTYPE = np.dtype([("unit", "<i4"), ("sub", "<i4"), ("row0", "<i4"), ("rows", "<i4")])
+assert ORTH_CHUNK_DTYPE.itemsize == 16
