@@ -60,13 +60,16 @@ struct OrthArgs {
 };
 
 constexpr int ORTH_THREADS = 256;
-constexpr int ORTH_CHUNK_FLOATS = 4096;  // rows per chunk = 4096 / RT (16 KiB of the factor)
+constexpr int ORTH_CHUNK_FLOATS = 2048;  // rows per chunk = 2048 / RT (8 KiB of the factor). The chunk
+                                         // is staged in shared memory as float64: conversions issue at
+                                         // a fraction of the FMA rate, so each value is converted once
+                                         // and not once per pair it takes part in
 
 // Sum over the rows of a chunk of a[row][j] * b[row][k] for every pair (j, k), in float64 and in
 // a fixed order: row groups stride through the chunk, then the groups are added in order.
 // Result: out[j * RT + k] (global scratch), written by the threads with tid < RT * RT.
 template <int RT>
-__device__ __forceinline__ void chunk_pairs(const float* sa, const float* sb, int rows, double* red, double* out, int tid) {
+__device__ __forceinline__ void chunk_pairs(const double* sa, const double* sb, int rows, double* red, double* out, int tid) {
   constexpr int NP = RT * RT;
   constexpr int PP = NP > ORTH_THREADS ? NP / ORTH_THREADS : 1;     // pairs per thread
   constexpr int NG = NP >= ORTH_THREADS ? 1 : ORTH_THREADS / NP;    // row groups
@@ -80,7 +83,7 @@ __device__ __forceinline__ void chunk_pairs(const float* sa, const float* sb, in
 #pragma unroll
     for (int q = 0; q < PP; ++q) {
       const int p = p0 + q * ORTH_THREADS;
-      acc[q] = fma((double)sa[row * RT + p / RT], (double)sb[row * RT + p % RT], acc[q]);
+      acc[q] = fma(sa[row * RT + p / RT], sb[row * RT + p % RT], acc[q]);
     }
   }
   if (NG == 1) {
@@ -107,23 +110,26 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_gram_kernel(OrthArgs a
   const int tid = threadIdx.x;
   const float* __restrict__ x = a.x + u.x_off;
 
-  __shared__ __align__(16) float sx[ORTH_CHUNK_FLOATS];
-  __shared__ __align__(16) float sf[ORTH_CHUNK_FLOATS];
+  __shared__ __align__(16) double sx[ORTH_CHUNK_FLOATS];
+  __shared__ __align__(16) double sf[ORTH_CHUNK_FLOATS];
   __shared__ double red[ORTH_THREADS];
   __shared__ double sG[NP];
   __shared__ int sDead[RT];      // -1: alive; >= 0: row of the substituted basis vector; -2: dropped
   __shared__ int s_last;
   // used by the finishing CTA only, after the staging buffers are dead
-  static_assert(NP * sizeof(double) <= ORTH_CHUNK_FLOATS * sizeof(float), "R must fit a staging buffer");
-  double* sR = reinterpret_cast<double*>(sf);      // upper-triangular Cholesky factor
-  double* sRinv = reinterpret_cast<double*>(sx);
+  static_assert(NP <= ORTH_CHUNK_FLOATS, "R must fit a staging buffer");
+  double* sR = sf;      // upper-triangular Cholesky factor
+  double* sRinv = sx;
+  __shared__ double sDiagInv[RT];                  // 1 / R[c][c]: float64 divisions and square roots
+                                                   // are long dependent instruction chains, so each
+                                                   // column pays for one and multiplies afterwards
 
   // ---- partial sums of this chunk ---------------------------------------------------------
   const int stride = 1 + a.nprev;
   double* my_part = a.part + (long long)blockIdx.x * stride * NP;
   for (int e = tid; e < ch.rows * RT; e += ORTH_THREADS) {
     const int row = e / RT, c = e % RT;
-    sx[e] = c < r ? x[(long long)(ch.row0 + row) * r + c] : 0.f;
+    sx[e] = c < r ? (double)x[(long long)(ch.row0 + row) * r + c] : 0.0;
   }
   __syncthreads();
   chunk_pairs<RT>(sx, sx, ch.rows, red, my_part, tid);
@@ -132,7 +138,7 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_gram_kernel(OrthArgs a
     __syncthreads();
     for (int e = tid; e < ch.rows * RT; e += ORTH_THREADS) {
       const int row = e / RT, c = e % RT;
-      sf[e] = c < r ? f[(long long)(ch.row0 + row) * r + c] : 0.f;
+      sf[e] = c < r ? (double)f[(long long)(ch.row0 + row) * r + c] : 0.0;
     }
     __syncthreads();
     chunk_pairs<RT>(sf, sx, ch.rows, red, my_part + (long long)(1 + p) * NP, tid);
@@ -181,13 +187,13 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_gram_kernel(OrthArgs a
       for (int c = 0; c < r; ++c) {
         // pivot of column c
         int attempt = 0;
-        double piv = 0.0;
+        double piv = 0.0, inv_piv = 0.0;
         while (true) {
           double s = sG[c * RT + c];
           for (int i = 0; i < c; ++i) s -= sR[i * RT + c] * sR[i * RT + c];
           const double ref = sG[c * RT + c];
           const bool ok = (ref > 0.0) && (s > 1e-12 * ref);
-          if (ok) { piv = sqrt(s); break; }
+          if (ok) { inv_piv = rsqrt(s); piv = s * inv_piv; break; }
           if (attempt == 2) { piv = 0.0; break; }
           // substitute column c by the basis vector e_row; its Gram entries are matrix entries
           const long long row = (attempt == 0 ? c : c + r) % len;
@@ -210,7 +216,7 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_gram_kernel(OrthArgs a
               if (sDead[i] == -2) { sR[i * RT + c] = 0.0; continue; }
               double t = sG[i * RT + c];
               for (int l = 0; l < i; ++l) t -= sR[l * RT + i] * sR[l * RT + c];
-              sR[i * RT + c] = t / sR[i * RT + i];
+              sR[i * RT + c] = t * sDiagInv[i];
             }
           }
           __syncwarp();
@@ -221,17 +227,21 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_gram_kernel(OrthArgs a
           if (lane == 0) {
             sDead[c] = -2;
             sR[c * RT + c] = 1.0;
+            sDiagInv[c] = 1.0;
             for (int i = 0; i < c; ++i) sR[i * RT + c] = 0.0;
           }
           __syncwarp();
           continue;  // row c of R stays zero right of the diagonal
         }
-        if (lane == 0) sR[c * RT + c] = piv;
+        if (lane == 0) {
+          sR[c * RT + c] = piv;
+          sDiagInv[c] = inv_piv;
+        }
         // row c of R, right of the diagonal: one lane per column
         for (int k = c + 1 + lane; k < r; k += 32) {
           double t = sG[c * RT + k];
           for (int i = 0; i < c; ++i) t -= sR[i * RT + c] * sR[i * RT + k];
-          sR[c * RT + k] = t / piv;
+          sR[c * RT + k] = t * inv_piv;
         }
         __syncwarp();
       }
@@ -240,7 +250,7 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_gram_kernel(OrthArgs a
         for (int i = c; i >= 0; --i) {
           double t = (i == c) ? 1.0 : 0.0;
           for (int k = i + 1; k <= c; ++k) t -= sR[i * RT + k] * sRinv[k * RT + c];
-          sRinv[i * RT + c] = t / sR[i * RT + i];
+          sRinv[i * RT + c] = t * sDiagInv[i];
         }
         if (sDead[c] == -2)
           for (int i = 0; i <= c; ++i) sRinv[i * RT + c] = 0.0;

@@ -200,7 +200,9 @@ class TilePlan:
         }
 
     TC_CTAS_PER_SM = 2
-    TC_TILE_OVERHEAD_ROWS = 96  # prologue + epilogue of a tile, in units of streamed K rows
+    # prologue + epilogue of a tile (~4 us), in units of streamed K rows (~0.03 us each): measured
+    # as rounds x (overhead + rows) over tile extents 512 ... 4096 on 4 x 4096^2
+    TC_TILE_OVERHEAD_ROWS = 136
 
     def _pick_tc_k(self, groups, transposed: bool) -> int:
         if not groups:
@@ -209,7 +211,8 @@ class TilePlan:
             return int(os.environ["PSGD_B200_TC_K"])  # tuning knob: fixed K extent (a multiple of 32)
         slots = 148 * self.TC_CTAS_PER_SM
         best, best_score = 512, -1.0
-        for k in range(256, 1024 + 1, 32):
+        longest = max((g.n if transposed else g.m) for g in groups)
+        for k in range(256, max(256, min(8192, -(-longest // 32) * 32)) + 1, 32):
             tiles = 0
             for g in groups:
                 k_len, out_len = (g.n, g.m) if transposed else (g.m, g.n)
