@@ -38,6 +38,7 @@ class TrainStep:
         eager_steps: int = 2,
         channels_last: bool = True,
         grad_clip: Optional[float] = None,
+        autotune: bool = True,
     ):
         self.model = model
         self.loss_fn = loss_fn
@@ -51,6 +52,11 @@ class TrainStep:
         self.channels_last = bool(channels_last) and self.device.type == "cuda"
         # optional global gradient-norm clipping before aggregation (the LSTM task clips at 0.4)
         self.grad_clip = grad_clip
+        # Shapes are static (the step is recorded once and replayed), so the library's
+        # convolution algorithms can be picked by measurement during the eager steps instead of
+        # by heuristics. Process-wide PyTorch switch; pass autotune=False to leave it alone.
+        if autotune and self.device.type == "cuda":
+            torch.backends.cudnn.benchmark = True
         self._steps_done = 0
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._static_x: Optional[torch.Tensor] = None
