@@ -379,6 +379,26 @@ def scenario_ddp_hooks_gloo():
         print("SCENARIO-OK")
 
 
+def scenario_preflight_gloo():
+    """The node preflight as CPU ranks: library all-reduce smoke test, one JSON report."""
+    from powersgd_b200.paper import environment
+
+    report = environment.main(backend="gloo")
+    assert report["ok"] and report["checks"]["library_all_reduce"] and report["world"] == dist.get_world_size()
+    if dist.get_rank() == 0:
+        print("SCENARIO-OK")
+
+
+def scenario_preflight():
+    """The node preflight on GPUs: adds peer access and the in-kernel all-reduce."""
+    from powersgd_b200.paper import environment
+
+    report = environment.main()
+    assert report["ok"] and report["checks"]["in_kernel_all_reduce"] and report["device"]["peer_access_to_all"]
+    if dist.get_rank() == 0:
+        print("SCENARIO-OK")
+
+
 if __name__ == "__main__":
     globals()["scenario_" + sys.argv[1]]()
     if dist.is_initialized():
