@@ -24,7 +24,7 @@ import torch.distributed as dist
 
 from .orthogonalization import orthogonalize
 from .plan import CompressionPlan, avg_compressed_size, matrix_shape, should_compress
-from .utils import allreduce_average, is_distributed, pack, unpack, world_size
+from .utils import allreduce_average, is_dense, is_distributed, pack, same_layout, unpack, world_size
 
 
 class Aggregator(ABC):
@@ -81,7 +81,7 @@ class AllReduce(Aggregator):
         if len(gradients) == 0:
             return []
         device = gradients[0].device
-        plain = all(g.dtype == torch.float32 and g.is_contiguous() for g in gradients)
+        plain = all(g.dtype == torch.float32 and is_dense(g) for g in gradients)
         if _pick_backend(self._backend_request, device) == "native" and plain:
             from .cuda_path import NativeFlatAllReduce
 
@@ -171,7 +171,10 @@ class PowerSGD(Aggregator):
             if any(seen) and not all(seen):
                 return False
             for p in group["params"]:
-                if p.dtype != torch.float32 or p.grad is None or not p.is_contiguous() or not p.grad.is_contiguous():
+                if p.dtype != torch.float32 or p.grad is None or not is_dense(p) or not same_layout(p.grad, p):
+                    return False
+                buf = optimizer.state.get(p, {}).get("momentum_buffer")
+                if buf is not None and not same_layout(buf, p):
                     return False
         return True
 
@@ -285,7 +288,7 @@ class BasicPowerSGD(Aggregator):
         if len(gradients) == 0:
             self.step_counter += 1
             return []
-        native_ok = self.dtype == torch.float32 and all(g.is_contiguous() and g.dtype == torch.float32 for g in gradients)
+        native_ok = self.dtype == torch.float32 and all(is_dense(g) and g.dtype == torch.float32 for g in gradients)
         if self.backend == "native" and native_ok:
             from .cuda_path import NativeCompressor
 
@@ -359,4 +362,8 @@ def batch_transpose(batch_of_matrices: torch.Tensor) -> torch.Tensor:
 def view_as_matrix(tensor: torch.Tensor) -> torch.Tensor:
     """[out features, everything else]; convolution kernels fold into the input features."""
     n, m = matrix_shape(tensor.shape)
+    if not tensor.is_contiguous() and is_dense(tensor):
+        # channels_last convolution weight: the same memory as a row-major matrix (its columns
+        # are a fixed permutation of the contiguous layout's, which the algorithm does not care about)
+        return tensor.as_strided((n, m), (m, 1))
     return tensor.view(n, m)

@@ -433,6 +433,7 @@ struct FlatArgs {
              // 3: local (no communication): out = grad / divisor, grad = 0 ; 4: local + SGD
              // 5: pack + push {value, epoch} words to every peer's slot (in-kernel all-reduce, part 1)
              // 6: poll the own slots, sum them in rank order -> out ; 7: same + SGD (part 2)
+             // 8: accumulate (out += grad; no communication, `flat` unused)
              // large buffers go two-shot (mode 0, then psgd_bulk_allreduce_launch on `flat`, which
              // is the data region of the arena, then one of):
              // 12: wait for the gathered chunks this block reads, then unpack ; 13: same + SGD
@@ -465,7 +466,8 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
   const PsgdHyper h = a.hyper[it.hyper];
   PsgdCommDev c;
   int e1 = 0;
-  if (a.mode >= 5) {
+  const bool uses_comm = a.mode >= 5 && a.mode != 8;
+  if (uses_comm) {
     c = *a.comm;
     e1 = *c.epoch + 1;
   }
@@ -476,7 +478,10 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
     const long long i = first + e;
     if (i >= it.numel) break;
     float g;
-    if (a.mode == 0) {
+    if (a.mode == 8) {
+      it.out[i] += it.grad[i];
+      continue;
+    } else if (a.mode == 0) {
       a.flat[it.flat_off + i] = it.grad[i] / a.divisor;
       it.grad[i] = 0.f;
       continue;
@@ -505,7 +510,7 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
       it.out[i] = g;
     }
   }
-  if (a.mode >= 6) psgd_comm_close_epoch(c, e1);  // the last consumer CTA advances the channel
+  if (uses_comm && a.mode >= 6) psgd_comm_close_epoch(c, e1);  // the last consumer CTA advances the channel
 }
 
 // Streaming variant of the modes that move whole buffers (0-4, 12, 13): four elements per access.
@@ -514,7 +519,10 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
 template <int MODE>
 __device__ __forceinline__ void flat_one(const FlatArgs& a, const PsgdFlat& it, const PsgdHyper& h, long long i) {
   float g;
-  if (MODE == 0) {
+  if (MODE == 8) {
+    it.out[i] += it.grad[i];
+    return;
+  } else if (MODE == 0) {
     a.flat[it.flat_off + i] = it.grad[i] / a.divisor;
     it.grad[i] = 0.f;
     return;
@@ -564,6 +572,14 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_vec_kernel(FlatArgs a)
     float4 g;
     float4* grad4 = (float4*)(it.grad + i);
     float4* flat4 = (float4*)(a.flat + it.flat_off + i);
+    if (MODE == 8) {
+      const float4 add = *grad4;
+      float4* o4 = (float4*)(it.out + i);
+      float4 o = *o4;
+      o.x += add.x; o.y += add.y; o.z += add.z; o.w += add.w;
+      *o4 = o;
+      continue;
+    }
     if (MODE == 0 || MODE == 3 || MODE == 4) {
       g = *grad4;
       // the scalar path divides; a multiplication by the reciprocal differs in the last bit for
@@ -618,11 +634,11 @@ PSGD_API int psgd_flat_launch(int mode, int vec, const void* items, const int* b
                               int nblocks, const void* hyper, float* flat, float divisor, const void* comm,
                               long long n_pad, cudaStream_t stream) {
   if (nblocks <= 0) return 0;
-  if (mode >= 5 && comm == nullptr) {
+  if (mode >= 5 && mode != 8 && comm == nullptr) {
     psgd_set_error("psgd_flat_launch: mode %d needs a communication channel", mode);
     return -1;
   }
-  if (!((mode >= 0 && mode <= 7) || mode == 12 || mode == 13)) {
+  if (!((mode >= 0 && mode <= 8) || mode == 12 || mode == 13)) {
     psgd_set_error("psgd_flat_launch: unknown mode %d", mode);
     return -1;
   }
@@ -643,6 +659,7 @@ PSGD_API int psgd_flat_launch(int mode, int vec, const void* items, const int* b
       case 2: flat_vec_launch<2>(a, nblocks, stream); break;
       case 3: flat_vec_launch<3>(a, nblocks, stream); break;
       case 4: flat_vec_launch<4>(a, nblocks, stream); break;
+      case 8: flat_vec_launch<8>(a, nblocks, stream); break;
       case 12: flat_vec_launch<12>(a, nblocks, stream); break;
       default: flat_vec_launch<13>(a, nblocks, stream); break;
     }

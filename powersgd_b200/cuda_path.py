@@ -29,7 +29,7 @@ import torch
 import torch.distributed as dist
 
 from .ops import layout, native
-from .utils import is_distributed, world_size
+from .utils import is_dense, is_distributed, like_strided, same_layout, world_size
 
 
 class _Range:
@@ -329,8 +329,12 @@ class NativeCompressor:
         if key == self._key:
             return
         for g in grads:
-            if not g.is_contiguous() or g.dtype != torch.float32 or g.device != self.device:
-                raise ValueError("native PowerSGD needs contiguous float32 gradients on its device")
+            if not is_dense(g) or g.dtype != torch.float32 or g.device != self.device:
+                raise ValueError("native PowerSGD needs dense float32 gradients on its device")
+        for name, others in (("parameters", params), ("momentum buffers", moms)):
+            for g, o in zip(grads, others or []):
+                if o is not None and not same_layout(o, g):
+                    raise ValueError(f"native PowerSGD needs {name} laid out like their gradients")
         if need_out and self._out_arena is None:
             self._out_arena = torch.empty(self.tiles.total_elems, device=self.device, dtype=torch.float32)
         where = self.plan.locate()
@@ -351,7 +355,7 @@ class NativeCompressor:
             d["mom"] = 0 if (moms is None or moms[idx] is None) else moms[idx].data_ptr()
             if need_out:
                 view = self._out_arena[out_offsets[idx] : out_offsets[idx] + grads[idx].numel()]
-                out_views[idx] = view.view(grads[idx].shape)
+                out_views[idx] = like_strided(view, grads[idx])
                 d["out"] = view.data_ptr()
             d["n"], d["m"], d["r"] = g.n, g.m, g.r
             d["p_off"] = g.p_offset + pos * g.n * g.r
@@ -682,15 +686,18 @@ class NativeFlatAllReduce:
         block_item, block_first = [], []
         views, cursor = [], 0
         for i, g in enumerate(grads):
-            if not g.is_contiguous() or g.dtype != torch.float32:
-                raise ValueError("native flat all-reduce needs contiguous float32 tensors")
+            if not is_dense(g) or g.dtype != torch.float32:
+                raise ValueError("native flat all-reduce needs dense float32 tensors")
+            for o in ((params[i] if params is not None else None), (moms[i] if moms is not None else None)):
+                if o is not None and not same_layout(o, g):
+                    raise ValueError("native flat all-reduce needs parameters and momentum buffers laid out like the gradients")
             it = items[i]
             it["grad"] = g.data_ptr()
             it["param"] = 0 if params is None else params[i].data_ptr()
             it["mom"] = 0 if (moms is None or moms[i] is None) else moms[i].data_ptr()
             if need_out:
                 v = self._out[cursor : cursor + g.numel()]
-                views.append(v.view(g.shape))
+                views.append(like_strided(v, g))
                 it["out"] = v.data_ptr()
             it["numel"] = g.numel()
             it["flat_off"] = cursor
@@ -802,6 +809,48 @@ class NativeFlatAllReduce:
         self._bulk_layout = None
 
 
+class MultiTensorAccumulate:
+    """`dst[i] += src[i]` for two lists of float32 tensors in ONE launch.
+
+    Error feedback keeps the compression residual in `p.grad` and lets autograd accumulate the
+    next gradient onto it (powersgd/__init__.py:17-25), which costs one small add kernel per
+    parameter. A training step that owns the loop detaches the residuals before backward, lets
+    autograd adopt the fresh gradients without arithmetic, and folds them in with this kernel."""
+
+    def __init__(self):
+        self.lib = native.lib()
+        self._key = None
+
+    def __call__(self, dst: Sequence[torch.Tensor], src: Sequence[torch.Tensor]) -> None:
+        key = (tuple(t.data_ptr() for t in dst), tuple(t.data_ptr() for t in src))
+        if key != self._key:
+            device = dst[0].device
+            per_block = self.lib.psgd_flat_block_elems()
+            items = np.zeros(len(dst), dtype=layout.FLAT_DTYPE)
+            block_item, block_first = [], []
+            for i, (d, s_) in enumerate(zip(dst, src)):
+                if not same_layout(d, s_) or d.dtype != torch.float32 or s_.dtype != torch.float32:
+                    raise ValueError("accumulate needs float32 tensors of equal shape and layout")
+                if not is_dense(d):
+                    raise ValueError("accumulate needs dense tensors")
+                items[i]["grad"], items[i]["out"], items[i]["numel"] = s_.data_ptr(), d.data_ptr(), d.numel()
+                for first in range(0, d.numel(), per_block):
+                    block_item.append(i)
+                    block_first.append(first)
+            self._vec = 1 if all(ptr % 16 == 0 for ptr in key[0] + key[1]) else 0
+            self._items = _to_device(items, device)
+            self._block_item = _to_device(np.asarray(block_item, dtype=np.int32), device)
+            self._block_first = _to_device(np.asarray(block_first, dtype=np.int32), device)
+            self._nblocks = len(block_item)
+            self._hyper = _to_device(NativeCompressor._default_hyper(), device)
+            self._key = key
+        code = self.lib.psgd_flat_launch(
+            8, self._vec, _ptr(self._items), _ptr(self._block_item), _ptr(self._block_first), self._nblocks,
+            _ptr(self._hyper), ctypes.c_void_p(0), 1.0, ctypes.c_void_p(0), ctypes.c_longlong(0), _stream_ptr(),
+        )
+        native.check(code, "psgd_flat_launch")
+
+
 class FusedSGDDriver:
     """Glue between `torch.optim.SGD` and the fused kernels.
 
@@ -847,7 +896,7 @@ class FusedSGDDriver:
                     if mu != 0.0:
                         st = optimizer.state[p]
                         if st.get("momentum_buffer") is None:
-                            st["momentum_buffer"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+                            st["momentum_buffer"] = torch.zeros_like(p)  # preserve_format: laid out like the parameter
                             fresh_groups.add(gi)
                         moms.append(st["momentum_buffer"])
                     else:

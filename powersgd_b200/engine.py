@@ -25,6 +25,7 @@ from typing import Callable, Dict, Optional
 import torch
 
 from .optim import optimizer_step
+from .utils import same_layout
 
 
 class TrainStep:
@@ -50,6 +51,8 @@ class TrainStep:
         # 4-D inputs are fed in NHWC: cuDNN's tensor-core convolutions run ~1.7x faster on
         # B200 that way, while parameters and their gradients stay contiguous [out, in*kh*kw].
         self.channels_last = bool(channels_last) and self.device.type == "cuda"
+        if self.channels_last:
+            self._weights_to_channels_last()
         # optional global gradient-norm clipping before aggregation (the LSTM task clips at 0.4)
         self.grad_clip = grad_clip
         # Shapes are static (the step is recorded once and replayed), so the library's
@@ -65,8 +68,28 @@ class TrainStep:
         self._pool = None
         self._agg_events = None
         self.launches_per_step = 0
+        # residuals detached from p.grad for the duration of backward: (parameter, residual)
+        self._held: list = []
+        self._accumulate = None
 
     # ------------------------------------------------------------------------------------
+    def _weights_to_channels_last(self) -> None:
+        """Store 4-D weights the way the NHWC convolutions read them. With contiguous weights the
+        library converts every filter before each forward / backward and converts every weight
+        gradient back (three small copy kernels per convolution and step). The aggregation
+        kernels take either layout: a channels_last weight is the same [out, in*kh*kw] matrix
+        with permuted columns."""
+        fmt = torch.channels_last
+        for p in self._params():
+            if p.dim() != 4 or p.is_contiguous(memory_format=fmt):
+                continue
+            p.data = p.data.contiguous(memory_format=fmt)
+            if p.grad is not None:
+                p.grad = p.grad.contiguous(memory_format=fmt)
+            buf = self.optimizer.state.get(p, {}).get("momentum_buffer")
+            if buf is not None:
+                self.optimizer.state[p]["momentum_buffer"] = buf.contiguous(memory_format=fmt)
+
     def _format(self, x: torch.Tensor) -> torch.Tensor:
         if self.channels_last and x.dim() == 4:
             return x.contiguous(memory_format=torch.channels_last)
@@ -87,16 +110,46 @@ class TrainStep:
         # Tensors that are all-reduced uncompressed leave no residual (their .grad is all zeros
         # after a step), so autograd does not need to ACCUMULATE onto it: dropping the zero tensor
         # lets it adopt the fresh gradient and saves one small add kernel per such tensor.
+        # Compressed tensors do leave a residual. It is detached for the duration of backward
+        # (autograd then adopts the fresh gradients without arithmetic) and `_fold` adds all
+        # fresh gradients onto their residuals in one launch instead of one add per parameter.
+        self._held = []
         mask = getattr(self.aggregator, "is_compressed_mask", None)
         if mask is not None and getattr(self.aggregator, "compressing", False):
+            fold = self.device.type == "cuda" and getattr(self.aggregator, "supports_fused_step", lambda _o: False)(self.optimizer)
             for p, keep in zip(self._params(), mask):
                 if not keep:
                     p.grad = None
+                elif fold and p.grad is not None:
+                    self._held.append((p, p.grad))
+                    p.grad = None
+
+    def _fold(self) -> None:
+        """p.grad <- residual + fresh gradient for the parameters detached by `_begin`."""
+        held, self._held = self._held, []
+        self._fold_launches = 0
+        if not held:
+            return
+        live = [(p, r) for p, r in held if p.grad is not None]
+        same = all(same_layout(p.grad, r) and p.grad.dtype == r.dtype for p, r in live)
+        if live and same and all(r.dtype == torch.float32 for _p, r in live):
+            if self._accumulate is None:
+                from .cuda_path import MultiTensorAccumulate
+
+                self._accumulate = MultiTensorAccumulate()
+            self._accumulate([r for _p, r in live], [p.grad for p, _r in live])
+            self._fold_launches = 1
+        else:
+            for p, r in live:
+                r.add_(p.grad)
+        for p, r in held:
+            p.grad = r  # parameters that received no gradient keep their residual as it was
 
     def _eager(self, x: torch.Tensor, y: torch.Tensor, time_aggregate: bool = False) -> torch.Tensor:
         self._begin()
         loss = self.loss_fn(self.model(self._format(x)), y)
         loss.backward()
+        self._fold()
         self._clip()
         if time_aggregate and self.device.type == "cuda":
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -108,7 +161,7 @@ class TrainStep:
             optimizer_step(self.optimizer, self.aggregator)
         fused = getattr(self.aggregator, "_fused", None)
         if fused is not None:
-            self.launches_per_step = getattr(fused, "launches", 0)
+            self.launches_per_step = getattr(fused, "launches", 0) + getattr(self, "_fold_launches", 0)
         return loss.detach()
 
     @property
@@ -152,6 +205,7 @@ class TrainStep:
             self._begin()
             loss = self.loss_fn(self.model(self._static_x), self._static_y)
             loss.backward()
+            self._fold()
             self._clip()
             agg.fused_step(self.optimizer, prepared=True)
             if self._static_loss is None:

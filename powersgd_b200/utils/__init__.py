@@ -30,6 +30,9 @@ __all__ = [
     "Timer",
     "DeviceTimer",
     "MeanAccumulator",
+    "is_dense",
+    "like_strided",
+    "same_layout",
 ]
 
 
@@ -91,3 +94,26 @@ def allreduce_average(data: torch.Tensor, *args, **kwargs):
         return SimpleNamespace(wait=lambda: None)
     data.div_(dist.get_world_size())
     return dist.all_reduce(data, *args, **kwargs)
+
+
+def is_dense(t: torch.Tensor) -> bool:
+    """The tensor's memory is one gap-free block whose first dimension is outermost: contiguous, or
+    a 4-D channels_last tensor (convolution weights stored [out, kh, kw, in]). Such a tensor is a
+    row-major [shape[0], numel / shape[0]] matrix in memory, which is all the kernels need; for
+    channels_last the matrix columns are a fixed permutation of the contiguous ones, which
+    PowerSGD is indifferent to."""
+    return t.is_contiguous() or (t.dim() == 4 and t.is_contiguous(memory_format=torch.channels_last))
+
+
+def same_layout(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Same shape and the same element order in memory (strides of size-1 dimensions are
+    arbitrary, e.g. a 1x1 convolution weight reports different strides per memory format)."""
+    if a.shape != b.shape:
+        return False
+    return all(n == 1 or sa == sb for n, sa, sb in zip(a.shape, a.stride(), b.stride()))
+
+
+def like_strided(flat_view: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
+    """View a flat run of `like.numel()` elements with the shape and strides of the dense `like`."""
+    return flat_view.as_strided(like.shape, like.stride())
+

@@ -183,3 +183,24 @@ def test_matches_reference_library_bitwise(rank, iters, steps):
             b.add_(n)
     assert torch.allclose(ours._powersgd._ps_buffer, theirs._powersgd._ps_buffer, atol=1e-5)
     assert torch.allclose(ours._powersgd._qs_buffer, theirs._powersgd._qs_buffer, atol=1e-5)
+
+
+def test_channels_last_weights_are_matrices_in_place():
+    """A channels_last convolution weight is the same row-major [out, rest] matrix in memory (with
+    permuted columns): the compressor works on it in place, and error feedback stays exact."""
+    from powersgd_b200.aggregators import view_as_matrix
+
+    torch.manual_seed(0)
+    w = torch.randn(16, 8, 3, 3, dtype=torch.float64).contiguous(memory_format=torch.channels_last)
+    m = view_as_matrix(w)
+    assert m.shape == (16, 72) and m.data_ptr() == w.data_ptr()
+    assert torch.equal(m[3], w[3].permute(1, 2, 0).reshape(-1))  # row = one filter, [kh, kw, in] order
+    grads = [w.clone(memory_format=torch.preserve_format), torch.randn(32, 16, 1, 1, dtype=torch.float64)]
+    assert not grads[0].is_contiguous()
+    original = [g.clone(memory_format=torch.preserve_format) for g in grads]
+    agg = BasicPowerSGD(grads, BasicConfig(rank=2, num_iters_per_step=2), backend="torch")
+    out = agg.aggregate(grads)
+    for o, g, ref in zip(out, grads, original):
+        assert o.shape == ref.shape
+        assert torch.allclose(o + g, ref, atol=1e-12)  # approximation + residual = gradient
+    assert float(grads[0].norm()) < float(original[0].norm())

@@ -211,3 +211,49 @@ def test_train_step_graph_matches_plain_loop():
         assert abs(a - b) < 1e-4 * max(1.0, abs(b)), (la, lb)
     for p, q in zip(ma.parameters(), mb.parameters()):
         assert _rel(p.detach(), q.detach()) < 1e-4
+
+
+def test_train_step_with_channels_last_weights_matches_plain_loop():
+    """TrainStep stores convolution weights channels_last, detaches the residuals during backward
+    and folds the fresh gradients in with one launch. The documented plain loop on a model in the
+    same layout (autograd accumulating onto p.grad) must follow the same trajectory."""
+    from powersgd_b200.engine import TrainStep
+
+    dev = torch.device("cuda:0")
+
+    def make():
+        torch.manual_seed(11)
+        model = torch.nn.Sequential(
+            torch.nn.Conv2d(3, 32, 3, padding=1, bias=False), torch.nn.BatchNorm2d(32), torch.nn.ReLU(),
+            torch.nn.Conv2d(32, 64, 3, padding=1, stride=2, bias=False), torch.nn.BatchNorm2d(64), torch.nn.ReLU(),
+            torch.nn.Conv2d(64, 64, 1, bias=False), torch.nn.ReLU(),
+            torch.nn.AdaptiveAvgPool2d(1), torch.nn.Flatten(), torch.nn.Linear(64, 10),
+        ).to(dev)
+        params = list(model.parameters())
+        opt = torch.optim.SGD(params, lr=0.05, momentum=0.9, nesterov=True, weight_decay=1e-4)
+        agg = PowerSGD(params, Config(rank=2, min_compression_rate=2, num_iters_per_step=2, start_compressing_after_num_steps=0))
+        return model, opt, agg
+
+    g = torch.Generator().manual_seed(1)
+    batches = [(torch.randn(16, 3, 16, 16, generator=g).to(dev), torch.randint(0, 10, (16,), generator=g).to(dev)) for _ in range(7)]
+    ma, oa, pa = make()
+    step = TrainStep(ma, torch.nn.functional.cross_entropy, oa, pa, cuda_graph=True, autotune=False)
+    la = [float(step(x, y).item()) for x, y in batches]
+    assert step._graphs, "never captured"
+    conv_weights = [p for p in ma.parameters() if p.dim() == 4 and p.shape[2] > 1]
+    assert conv_weights and all(not p.is_contiguous() and not p.grad.is_contiguous() for p in conv_weights)
+    mb, ob, pb = make()
+    mb.to(memory_format=torch.channels_last)
+    lb = []
+    for x, y in batches:
+        loss = torch.nn.functional.cross_entropy(mb(x.contiguous(memory_format=torch.channels_last)), y)
+        loss.backward()
+        optimizer_step(ob, pb)
+        lb.append(float(loss.item()))
+    for a, b in zip(la, lb):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(b)), (la, lb)
+    for p, q in zip(ma.parameters(), mb.parameters()):
+        assert _rel(p.detach(), q.detach()) < 2e-3
+    # the residual stays in p.grad, as the plain loop leaves it
+    for p, q in zip(ma.parameters(), mb.parameters()):
+        assert _rel(p.grad, q.grad) < 5e-3 or float(q.grad.abs().max()) == 0.0
