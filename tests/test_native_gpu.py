@@ -257,3 +257,9 @@ def test_train_step_with_channels_last_weights_matches_plain_loop():
     # the residual stays in p.grad, as the plain loop leaves it
     for p, q in zip(ma.parameters(), mb.parameters()):
         assert _rel(p.grad, q.grad) < 5e-3 or float(q.grad.abs().max()) == 0.0
+    # batch-norm state: counters advance once per step (eager and replayed alike), statistics follow
+    for (name, ba), (_n, bb) in zip(ma.named_buffers(), mb.named_buffers()):
+        if ba.dtype == torch.long:
+            assert int(ba) == int(bb) == len(batches), name
+        else:
+            assert _rel(ba, bb) < 2e-3, name
