@@ -40,6 +40,12 @@ constexpr int TC_A_BYTES = TC_TILE * TC_BK * 4;   // 16 KiB
 constexpr int TC_STAGES = 4;      // landing ring of the gradient tile (TMA -> shared memory)
 constexpr int TC_OP_STAGES = 2;   // ring of the operands the converters write (A_lo, factor slab):
                                   // shallower than the landing ring, two CTAs still fit one SM
+constexpr int TC_SEG = 16;        // stages (512 K rows) accumulated in TMEM before the sum moves to registers:
+                                  // the tensor core adds into its FP32 accumulator with truncation, a bias
+                                  // that grows with the length of the chain (measured against the FP64
+                                  // product: 5e-7 relative for 512 rows, 1e-5 for 2048, 6e-5 for 6272). Two
+                                  // accumulators alternate, so the MMA stream never waits for the hand-over.
+constexpr int TC_DRAIN_LAG = 2;   // stages converted into the next segment before the finished one is read
 constexpr uint64_t TC_WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 struct TcArgs {
@@ -161,7 +167,7 @@ template <bool TRANSPOSED, int RP, bool SPLIT>
 __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_constant__ TcArgs a) {
   constexpr int N2 = ((SPLIT ? 2 : 1) * RP) < 16 ? 16 : ((SPLIT ? 2 : 1) * RP);
   constexpr int B_BYTES = N2 * 128;
-  constexpr int TMEM_COLS = N2 <= 32 ? 32 : 64;
+  constexpr int TMEM_COLS = 2 * N2 < 32 ? 32 : 2 * N2;   // two accumulators of N2 columns
   constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((TRANSPOSED ? 1u : 0u) << 15) |
                              ((uint32_t)(N2 >> 3) << 17) | ((uint32_t)(TC_TILE >> 4) << 24);
 
@@ -178,7 +184,9 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
   uint8_t* sB = sAlo + (SPLIT ? TC_OP_STAGES * TC_A_BYTES : 0);  // [OP_STAGES][B_BYTES]
   // full: tile landed (TMA -> converters); ready: A_lo and factor slab written (converters -> MMA);
   // empty: landing slot consumed (MMA -> TMA); op_empty: operand slot consumed (MMA -> converters)
-  __shared__ __align__(8) uint64_t bar_full[TC_STAGES], bar_empty[TC_STAGES], bar_ready[TC_OP_STAGES], bar_op_empty[TC_OP_STAGES], bar_accum;
+  // seg: the MMAs of a segment are complete (MMA -> converters); drained: its accumulator was read
+  __shared__ __align__(8) uint64_t bar_full[TC_STAGES], bar_empty[TC_STAGES], bar_ready[TC_OP_STAGES], bar_op_empty[TC_OP_STAGES];
+  __shared__ __align__(8) uint64_t bar_seg[2], bar_drained[2];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort, s_last;
 
@@ -199,7 +207,10 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
       mbar_init(&bar_ready[s], 128);
       mbar_init(&bar_op_empty[s], 1);
     }
-    mbar_init(&bar_accum, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bar_seg[b], 1);
+      mbar_init(&bar_drained[b], 128);
+    }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -212,6 +223,26 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = s_tmem;
   volatile int* abort_flag = &s_abort;
+  // warps 0-3: running FP32 sum of the finished segments of accumulator row (warp * 32 + lane)
+  float sum[N2];
+#pragma unroll
+  for (int i = 0; i < N2; ++i) sum[i] = 0.f;
+  const int nseg = (nk + TC_SEG - 1) / TC_SEG;
+  int next_drain = 0;
+  bool drain_ok = true;
+  auto drain = [&](int g) {
+    // segment g used accumulator (g & 1) for the (g >> 1)-th time
+    if (drain_ok) drain_ok = mbar_wait(&bar_seg[g & 1], (g >> 1) & 1, abort_flag, a.status);
+    if (drain_ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float d[N2];
+      tmem_load_row<N2>(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((g & 1) * N2), d);
+#pragma unroll
+      for (int i = 0; i < N2; ++i) sum[i] += d[i];
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    mbar_arrive(&bar_drained[g & 1]);
+  };
 
   if (warp == 4) {
     // ---------------- TMA producer ----------------
@@ -238,9 +269,15 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
       bool ok = true;
       for (int kb = 0; kb < nk && ok; ++kb) {
         const int s = kb % TC_STAGES, so = kb % TC_OP_STAGES;
+        const int g = kb / TC_SEG;
+        const bool seg_first = kb % TC_SEG == 0;
+        // accumulator (g & 1) was last used by segment g - 2: wait until the converters have read it
+        if (seg_first && g >= 2) ok = mbar_wait(&bar_drained[g & 1], ((g >> 1) - 1) & 1, abort_flag, a.status);
+        if (!ok) break;
         ok = mbar_wait(&bar_ready[so], (kb / TC_OP_STAGES) & 1, abort_flag, a.status);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem + (uint32_t)((g & 1) * N2);
         const uint32_t aaddr = smem_u32(sA + s * TC_A_BYTES);
         const uint32_t laddr = smem_u32(sAlo + so * TC_A_BYTES);
         const uint32_t baddr = smem_u32(sB + so * B_BYTES);
@@ -251,16 +288,16 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
           // NN (K-major A): 8 K floats = 32 bytes further along each 128-byte row, row groups 1 KiB apart.
           const uint64_t da = TRANSPOSED ? umma_desc(aaddr + ks * 1024, 4096, 512, 1) : umma_desc(aaddr + ks * 32, 16, 1024);
           const uint64_t db = umma_desc(baddr + ks * 32, 16, 1024);
-          umma_tf32(tmem, da, db, IDESC, (kb | ks) != 0 ? 1u : 0u);
+          umma_tf32(acc, da, db, IDESC, (seg_first && ks == 0) ? 0u : 1u);
           if (SPLIT) {
             const uint64_t dl = TRANSPOSED ? umma_desc(laddr + ks * 1024, 4096, 512, 1) : umma_desc(laddr + ks * 32, 16, 1024);
-            umma_tf32(tmem, dl, db, IDESC, 1u);
+            umma_tf32(acc, dl, db, IDESC, 1u);
           }
         }
         umma_commit(&bar_empty[s]);      // frees the landing slot once these MMAs have read it
         umma_commit(&bar_op_empty[so]);  // and the operand slot
+        if (kb % TC_SEG == TC_SEG - 1 || kb == nk - 1) umma_commit(&bar_seg[g & 1]);  // segment complete
       }
-      umma_commit(&bar_accum);        // accumulator complete (or abandoned)
     }
   } else {
     // ---------------- converters (then epilogue) ----------------
@@ -318,23 +355,19 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(&bar_ready[so]);
+      // a finished segment is read a couple of stages later, when its MMAs are certainly done
+      while (next_drain < nseg - 1 && kb >= (next_drain + 1) * TC_SEG - 1 + TC_DRAIN_LAG) drain(next_drain++);
     }
+    while (next_drain < nseg) drain(next_drain++);
   }
 
   // ---------------- epilogue ----------------
   float* sSum = reinterpret_cast<float*>(base);  // [128][RP], aliases stage 0 once the MMAs are done
-  bool accum_ok = true;
   if (warp < 4) {
-    accum_ok = mbar_wait(&bar_accum, 0, abort_flag, a.status);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    float d[N2];
-    if (accum_ok) tmem_load_row<N2>(tmem + ((uint32_t)(warp * 32) << 16), d);
-    else {
+    // all segments are in registers (the last drain waited for the last MMAs, so no stage of
+    // shared memory is read any more and sSum may alias it)
 #pragma unroll
-      for (int i = 0; i < N2; ++i) d[i] = 0.f;
-    }
-#pragma unroll
-    for (int n = 0; n < RP; ++n) sSum[tid * RP + n] = SPLIT ? d[n] + d[n + RP] : d[n];
+    for (int n = 0; n < RP; ++n) sSum[tid * RP + n] = SPLIT ? sum[n] + sum[n + RP] : sum[n];
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
