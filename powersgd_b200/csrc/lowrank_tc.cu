@@ -33,7 +33,9 @@
 
 namespace {
 
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;     // warps 0-3: converters + epilogue, 4: TMA, 5: MMA, 6-9: converters
+constexpr int TC_NCONV = 256;       // converter threads: the conversion pass, not the memory system,
+                                    // paced the pipeline with four warps
 constexpr int TC_BK = 32;           // K elements (floats) per stage
 constexpr int TC_TILE = 128;        // output rows of the accumulator (UMMA M)
 constexpr int TC_A_BYTES = TC_TILE * TC_BK * 4;   // 16 KiB
@@ -164,7 +166,7 @@ __device__ __forceinline__ void tmem_load_row<64>(uint32_t taddr, float* v) {
 
 // RP: factor rank padded to 8 / 16 / 32. N of the MMA is max(16, (SPLIT ? 2 : 1) * RP).
 template <bool TRANSPOSED, int RP, bool SPLIT>
-__global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_constant__ TcArgs a) {
+__global__ void __launch_bounds__(TC_THREADS, 2) psgd_gemm_tc_kernel(const __grid_constant__ TcArgs a) {
   constexpr int N2 = ((SPLIT ? 2 : 1) * RP) < 16 ? 16 : ((SPLIT ? 2 : 1) * RP);
   constexpr int B_BYTES = N2 * 128;
   constexpr int TMEM_COLS = 2 * N2 < 32 ? 32 : 2 * N2;   // two accumulators of N2 columns
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
       mbar_init(&bar_empty[s], 1);
     }
     for (int s = 0; s < TC_OP_STAGES; ++s) {
-      mbar_init(&bar_ready[s], 128);
+      mbar_init(&bar_ready[s], TC_NCONV);
       mbar_init(&bar_op_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -301,16 +303,17 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
     }
   } else {
     // ---------------- converters (then epilogue) ----------------
+    const int ctid = warp < 4 ? tid : tid - 64;   // index among the converter threads
     const float* __restrict__ fac = a.in + (TRANSPOSED ? mt.p_off : mt.q_off);
     // each thread stages RP / 4 factor values per stage; they are fetched one stage ahead so
     // that their L2 latency hides behind the wait for the gradient tile
-    constexpr int PER_THREAD = TC_BK * RP / 128;
+    constexpr int PER_THREAD = TC_BK * RP / TC_NCONV;
     float pre[PER_THREAD];
     auto fetch = [&](int kb) {
       const int k0 = k_begin + kb * TC_BK;
 #pragma unroll
       for (int i = 0; i < PER_THREAD; ++i) {
-        const int e = tid + i * 128;
+        const int e = ctid + i * TC_NCONV;
         const int k = e / RP, n = e % RP;
         float v = 0.f;
         if (kb < nk && n < r && k0 + k < k_limit && kb * TC_BK + k < k_len) v = __ldg(fac + (long long)(k0 + k) * r + n);
@@ -331,16 +334,16 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
         const float4* src = reinterpret_cast<const float4*>(sA + s * TC_A_BYTES);
         float4* dst = reinterpret_cast<float4*>(sAlo + so * TC_A_BYTES);
 #pragma unroll
-        for (int i = 0; i < TC_A_BYTES / 16 / 128; ++i) {
-          const float4 v = src[tid + i * 128];
-          dst[tid + i * 128] = make_float4(v.x - tf32_hi(v.x), v.y - tf32_hi(v.y), v.z - tf32_hi(v.z), v.w - tf32_hi(v.w));
+        for (int i = 0; i < TC_A_BYTES / 16 / TC_NCONV; ++i) {
+          const float4 v = src[ctid + i * TC_NCONV];
+          dst[ctid + i * TC_NCONV] = make_float4(v.x - tf32_hi(v.x), v.y - tf32_hi(v.y), v.z - tf32_hi(v.z), v.w - tf32_hi(v.w));
         }
       }
       // factor slab: B[n][k] for k in this stage, K-major rows of 128 bytes with 128-byte swizzle
       uint8_t* bt = sB + so * B_BYTES;
 #pragma unroll
       for (int i = 0; i < PER_THREAD; ++i) {
-        const int e = tid + i * 128;
+        const int e = ctid + i * TC_NCONV;
         const int k = e / RP, n = e % RP;
         const float v = cur[i];
         const float hi = tf32_hi(v);
@@ -350,15 +353,15 @@ __global__ void __launch_bounds__(TC_THREADS) psgd_gemm_tc_kernel(const __grid_c
       }
       if ((SPLIT ? 2 : 1) * RP < N2) {
         // pad rows of B (only when RP = 8 without split): zero
-        for (int e = tid; e < (N2 - (SPLIT ? 2 : 1) * RP) * 32; e += 128)
+        for (int e = ctid; e < (N2 - (SPLIT ? 2 : 1) * RP) * 32; e += TC_NCONV)
           reinterpret_cast<float*>(bt + (SPLIT ? 2 : 1) * RP * 128)[e] = 0.f;
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(&bar_ready[so]);
       // a finished segment is read a couple of stages later, when its MMAs are certainly done
-      while (next_drain < nseg - 1 && kb >= (next_drain + 1) * TC_SEG - 1 + TC_DRAIN_LAG) drain(next_drain++);
+      while (warp < 4 && next_drain < nseg - 1 && kb >= (next_drain + 1) * TC_SEG - 1 + TC_DRAIN_LAG) drain(next_drain++);
     }
-    while (next_drain < nseg) drain(next_drain++);
+    while (warp < 4 && next_drain < nseg) drain(next_drain++);
   }
 
   // ---------------- epilogue ----------------
