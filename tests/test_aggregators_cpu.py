@@ -204,3 +204,22 @@ def test_channels_last_weights_are_matrices_in_place():
         assert o.shape == ref.shape
         assert torch.allclose(o + g, ref, atol=1e-12)  # approximation + residual = gradient
     assert float(grads[0].norm()) < float(original[0].norm())
+
+
+def test_dense_layout_helpers():
+    from powersgd_b200.utils import is_dense, like_strided, same_layout
+
+    a = torch.randn(8, 4, 3, 3)
+    cl = a.contiguous(memory_format=torch.channels_last)
+    assert is_dense(a) and is_dense(cl) and not is_dense(a[:, ::2]) and not is_dense(a.permute(1, 0, 2, 3))
+    assert same_layout(a, torch.empty_like(a)) and same_layout(cl, torch.empty_like(cl)) and not same_layout(a, cl)
+    # a 1x1 convolution weight is the same memory in both formats although its strides differ
+    w = torch.randn(16, 8, 1, 1)
+    w_cl = w.contiguous(memory_format=torch.channels_last)
+    assert same_layout(w, w_cl) and is_dense(w_cl)
+    assert not same_layout(a, torch.randn(8, 4, 3, 2))
+    # a flat run viewed like a channels_last tensor holds the elements in that tensor's memory order
+    flat = torch.arange(cl.numel(), dtype=torch.float32)
+    v = like_strided(flat, cl)
+    assert v.shape == cl.shape and v.stride() == cl.stride() and v.data_ptr() == flat.data_ptr()
+    assert v[0, 1, 0, 0] == 1 and v[0, 0, 0, 1] == 4  # channel is the fastest dimension
