@@ -7,7 +7,7 @@ from test_dist_cpu import run_scenario
 pytestmark = pytest.mark.gpu
 
 needs_two = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-# plain peer stores only; keep the library's in-switch multicast out of these runs
+# plain peer stores only; keep the library's NVLS (in-switch reduction) path out of these runs
 ENV = {"NCCL_NVLS_ENABLE": "0"}
 
 
