@@ -29,7 +29,7 @@ import torch
 import torch.distributed as dist
 
 from .ops import layout, native
-from .utils import is_dense, is_distributed, like_strided, same_layout, world_size
+from .utils import is_dense, like_strided, same_layout, world_size
 
 
 class _Range:

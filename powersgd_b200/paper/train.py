@@ -25,7 +25,6 @@ from __future__ import annotations
 import datetime
 import os
 import re
-import time
 
 import numpy as np
 import torch

@@ -1,6 +1,5 @@
 """Every architecture of the zoo builds, runs a 32 x 32 batch and matches the upstream
 definition's parameter names and shapes (when the upstream research code is available)."""
-import importlib.util
 import os
 import sys
 

@@ -1,5 +1,4 @@
 """Native sm_100a kernels against the PyTorch float32/float64 restatement of the same ops."""
-import copy
 
 import pytest
 import torch

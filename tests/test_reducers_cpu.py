@@ -2,7 +2,6 @@
 upstream implementation."""
 import importlib.util
 import os
-import sys
 
 import numpy as np
 import pytest
