@@ -219,6 +219,9 @@ def test_train_step_with_channels_last_weights_matches_plain_loop():
     from powersgd_b200.engine import TrainStep
 
     dev = torch.device("cuda:0")
+    # an earlier TrainStep in this process may have switched convolution autotuning on; both arms
+    # of this comparison must run the same deterministic algorithm choice
+    torch.backends.cudnn.benchmark = False
 
     def make():
         torch.manual_seed(11)
