@@ -326,6 +326,7 @@ def main():
                 "wall_ms_per_step": wall_ms / args.steps,
                 "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4,
+                "loss_read": "copied to pinned host memory every step, read on the host after the next step is enqueued",
                 "last_loss": last,
             },
             "gpu_launches": launches,
