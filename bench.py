@@ -11,7 +11,11 @@ momentum 0.9 and weight decay 1e-4. One process per GPU; weak scaling.
 Prints ONE JSON line on rank 0. `value` is device-timed (CUDA events around exactly K steps,
 max over ranks) with the inputs already resident on the GPU; `e2e.value` times the same K
 steps through the public API including, every step, the host->device copy of that step's
-batch from pinned memory and the device->host read of the loss.
+batch from pinned memory and the device->host read of the loss. `aggregate_ms_per_step` is
+the second half of the metric (compress + reduce + optimizer update): the device time from
+the end of backward to the end of the parameter update, averaged over further steps after the
+two timed regions, max over ranks - for this library read from two event-record nodes inside
+the replayed CUDA graph, for the reference from an event pair around its `optimizer_step`.
 
 `--impl reference` runs the unmodified upstream package (installed under baseline/_ref) with
 the upstream model definition and `powersgd.optimizer_step`; nothing of this repository's
@@ -181,11 +185,21 @@ def build_reference(device):
 
     class Step:
         launches_per_step = 0
+        time_aggregate = False   # switched on for the separate aggregate-timing pass only
+        aggregate_ms = None
 
         def __call__(self, x, y):
             loss = torch.nn.functional.cross_entropy(model(x), y)
             loss.backward()
-            ref.optimizer_step(optimizer, aggregator)
+            if self.time_aggregate:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                ref.optimizer_step(optimizer, aggregator)
+                b.record()
+                b.synchronize()
+                self.aggregate_ms = a.elapsed_time(b)
+            else:
+                ref.optimizer_step(optimizer, aggregator)
             return loss.detach()
 
     return Step()
@@ -288,6 +302,20 @@ def main():
     e2e_ms = max_over_ranks(max(e_start.elapsed_time(e_stop), 0.0))
     clocks = sampler.stop()
 
+    # ---- compress + reduce + update time per step, steady state (outside both timed regions) ----
+    agg_steps = max(10, min(100, args.steps))
+    if args.impl == "reference":
+        step.time_aggregate = True
+    agg_samples = []
+    for i in range(agg_steps):
+        step(xs_dev[i % n_slots], ys_dev[i % n_slots])
+        torch.cuda.synchronize()
+        ms = step.aggregate_ms
+        if ms is not None:
+            agg_samples.append(ms)
+    agg_ms = max_over_ranks(sum(agg_samples) / len(agg_samples)) if agg_samples else None
+    barrier()
+
     images = BATCH_PER_GPU * world * args.steps
     h2d = xs_host[0].numel() * xs_host[0].element_size() + ys_host[0].numel() * ys_host[0].element_size()
     launches = getattr(step, "launches_per_step", 0) * args.steps
@@ -315,9 +343,8 @@ def main():
                              "start_compressing_after_num_steps": 0},
                 "optimizer": {"sgd_lr": LR, "momentum": MOMENTUM, "nesterov": True, "weight_decay": WD},
                 "l2": "per-step working set (activations + gradients, > 1 GB at batch 128) exceeds the 126 MB L2; no explicit flush",
-                "cuda_graph": bool(args.impl == "ours" and not args.no_graph),
-                "host_cpus": os.cpu_count(),
             },
+            "engine": {"cuda_graph": bool(args.impl == "ours" and not args.no_graph), "host_cpus": os.cpu_count()},
             "clocks": clocks,
             "e2e": {
                 "value": images / (e2e_ms / 1e3),
@@ -330,7 +357,13 @@ def main():
                 "last_loss": last,
             },
             "gpu_launches": launches,
-            "aggregate_ms_per_step": getattr(step, "aggregate_ms", None),
+            "aggregate_ms_per_step": agg_ms,
+            "aggregate_how": (
+                f"device time from the end of backward to the end of the parameter update, mean of {len(agg_samples)} "
+                "steady-state steps after the timed regions, max over ranks; "
+                + ("event-record nodes inside the replayed CUDA graph" if args.impl == "ours" and not args.no_graph
+                   else "CUDA-event pair around the aggregation + optimizer call")
+            ),
         }
         print(json.dumps(out))
     if world > 1:

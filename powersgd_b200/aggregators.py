@@ -30,7 +30,10 @@ from .utils import allreduce_average, is_dense, is_distributed, pack, same_layou
 class Aggregator(ABC):
     @abstractmethod
     def aggregate(self, gradients: List[torch.Tensor]) -> List[torch.Tensor]:
-        """Return averaged gradients; overwrite the inputs with what was NOT communicated."""
+        """Return averaged gradients; overwrite the inputs with what was NOT communicated.
+
+        With the native back end the returned tensors are views into an arena that the NEXT call
+        overwrites (the reference returns fresh tensors): clone what must outlive a step."""
 
 
 class Config(NamedTuple):
@@ -163,6 +166,9 @@ class PowerSGD(Aggregator):
             return False
         if _pick_backend(self._backend_request, self.device) != "native":
             return False
+        # the fused path never calls optimizer.step(): registered step hooks would not fire
+        if getattr(optimizer, "_optimizer_step_pre_hooks", None) or getattr(optimizer, "_optimizer_step_post_hooks", None):
+            return False
         for group in optimizer.param_groups:
             if group.get("maximize", False) or group.get("differentiable", False):
                 return False
@@ -208,6 +214,8 @@ class PowerSGD(Aggregator):
         if getattr(self, "_fused", None) is None:
             self._fused = FusedSGDDriver(self)
         self._fused.step(optimizer, prepared=prepared)
+        # what a learning-rate scheduler looks at to tell that the optimizer has stepped
+        optimizer._opt_called = True
 
     def state_dict(self, gradients: Optional[Sequence[torch.Tensor]] = None) -> Dict:
         from .state import aggregator_state_dict

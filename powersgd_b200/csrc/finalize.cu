@@ -30,7 +30,58 @@ struct FinalizeArgs {
   const float* rsum[PSGD_MAX_HIST];
   float inv_world;
   int fused_sgd;
+  // Multi-GPU, strip kernel only: the summed factor of the LAST half-iteration has not been
+  // gathered yet. The panels of lsum[nhist-1] (poll_left != 0) or rsum[nhist-1] are then read
+  // from the channel's slots (bounded polls, ranks added in order); the strips that touch column
+  // 0 (left factor) or row 0 (right factor) also write the sum to sum_out1 / sum_out2, which are
+  // laid out like the factor buffers. Null comm: every panel comes from memory.
+  const PsgdCommDev* comm;
+  int poll_left;
+  float* sum_out1;
+  float* sum_out2;
 };
+
+// Column ownership of a lane inside a 128-column block, by access width (see lowrank_ffma.cu).
+template <int VEC>
+__device__ __forceinline__ int fin_lane_col(int lane, int c) {
+  if (VEC == 4) return 4 * lane + c;
+  if (VEC == 2) return (c < 2) ? 2 * lane + c : 64 + 2 * lane + (c - 2);
+  return lane + 32 * c;
+}
+// Position of local column lc in a panel row, such that a lane's 4 columns are adjacent.
+template <int VEC>
+__device__ __forceinline__ int fin_panel_pos(int lc) {
+  if (VEC == 4) return lc;
+  if (VEC == 2) return ((lc & 63) >> 1) * 4 + (lc & 1) + 2 * (lc >> 6);
+  return (lc & 31) * 4 + (lc >> 5);
+}
+// The lane's 4 elements of a row (block starts at `p`, `cols` valid): load / store.
+template <int VEC>
+__device__ __forceinline__ void fin_load4(const float* p, int lane, int cols, float* v) {
+  if (VEC == 4) {
+    if (lane * 4 < cols) *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(p + lane * 4);
+  } else if (VEC == 2) {
+    if (lane * 2 < cols) *reinterpret_cast<float2*>(v) = *reinterpret_cast<const float2*>(p + lane * 2);
+    if (64 + lane * 2 < cols) *reinterpret_cast<float2*>(v + 2) = *reinterpret_cast<const float2*>(p + 64 + lane * 2);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      if (lane + 32 * c < cols) v[c] = p[lane + 32 * c];
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void fin_store4(float* p, int lane, int cols, const float* v) {
+  if (VEC == 4) {
+    if (lane * 4 < cols) *reinterpret_cast<float4*>(p + lane * 4) = *reinterpret_cast<const float4*>(v);
+  } else if (VEC == 2) {
+    if (lane * 2 < cols) *reinterpret_cast<float2*>(p + lane * 2) = *reinterpret_cast<const float2*>(v);
+    if (64 + lane * 2 < cols) *reinterpret_cast<float2*>(p + 64 + lane * 2) = *reinterpret_cast<const float2*>(v + 2);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      if (lane + 32 * c < cols) p[lane + 32 * c] = v[c];
+  }
+}
 
 __device__ __forceinline__ float psgd_sgd_update(float g, float& p, float* mom_ptr, const PsgdHyper& h) {
   // torch.optim.SGD semantics: weight decay folded into the gradient, then momentum.
@@ -49,9 +100,9 @@ __device__ __forceinline__ float psgd_sgd_update(float g, float& p, float* mom_p
 // removed from the gradient: one accumulator, half the shared-memory traffic and FMAs.
 // General kernel (any K): panels of FIN_KC factor columns are re-staged for every 32-row chunk.
 template <int VEC, bool SAME>
-__global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs a) {
-  const PsgdTile whole = a.tiles[blockIdx.x];
-  const PsgdMat mt = a.mats[whole.mat];
+__device__ __forceinline__ void finalize_general_tile(const FinalizeArgs& a, const PsgdTile& whole, const PsgdMat& mt,
+                                                      float (*sLl)[FIN_ROWS], float (*sLs)[FIN_ROWS],
+                                                      float (*sRl)[FIN_COLS], float (*sRs)[FIN_COLS]) {
   for (int rc = 0; rc < whole.rows; rc += FIN_ROWS) {
   PsgdTile t = whole;
   t.row0 = whole.row0 + rc;
@@ -60,11 +111,6 @@ __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs
   const int r = mt.r, m = mt.m;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = a.nhist * r;
-
-  __shared__ __align__(16) float sLl[FIN_KC][FIN_ROWS];
-  __shared__ __align__(16) float sLs[FIN_KC][FIN_ROWS];
-  __shared__ __align__(16) float sRl[FIN_KC][FIN_COLS];
-  __shared__ __align__(16) float sRs[FIN_KC][FIN_COLS];
 
   float accE[4][4], accA[4][4];
 #pragma unroll
@@ -110,8 +156,8 @@ __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs
         vl = a.rloc[h][off];
         if (!SAME) vs = a.rsum[h][off];
       }
-      // lane-major placement so that each lane's 4 columns are adjacent for VEC == 4
-      const int pos = (VEC == 4) ? lc : ((lc & 31) * 4 + (lc >> 5));
+      // lane-major placement so that each lane's 4 columns are adjacent
+      const int pos = fin_panel_pos<VEC>(lc);
       sRl[kk][pos] = vl;
       if (!SAME) sRs[kk][pos] = vs;
     }
@@ -141,61 +187,46 @@ __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs
       for (int c = 0; c < 4; ++c) accA[u][c] = accE[u][c];
   }
   const PsgdHyper h = a.hyper[mt.hyper];
+  const bool sgd = a.fused_sgd != 0;
+  const bool mom = sgd && h.has_momentum;
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     const int lr = warp * 4 + u;
     if (lr >= t.rows) continue;
-    const long long rowoff = (long long)(t.row0 + lr) * m;
-    if (VEC == 4) {
-      const int col = t.col0 + lane * 4;
-      if (lane * 4 >= t.cols) continue;
-      const float4 g = SAME ? gpre[u] : *reinterpret_cast<const float4*>(mt.grad + rowoff + col);
-      float gv[4] = {g.x, g.y, g.z, g.w};
-      float av[4];
+    const long long rowoff = (long long)(t.row0 + lr) * m + t.col0;
+    __align__(16) float gv[4] = {0.f, 0.f, 0.f, 0.f}, pv[4] = {0.f, 0.f, 0.f, 0.f}, mv[4] = {0.f, 0.f, 0.f, 0.f}, av[4];
+    if (VEC == 4 && SAME) *reinterpret_cast<float4*>(gv) = gpre[u];
+    else fin_load4<VEC>(mt.grad + rowoff, lane, t.cols, gv);
+    if (sgd) fin_load4<VEC>(mt.param + rowoff, lane, t.cols, pv);
+    if (mom) fin_load4<VEC>(mt.mom + rowoff, lane, t.cols, mv);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        gv[c] -= accE[u][c];
-        av[c] = accA[u][c] * a.inv_world;
-      }
-      *reinterpret_cast<float4*>(mt.grad + rowoff + col) = make_float4(gv[0], gv[1], gv[2], gv[3]);
-      if (a.fused_sgd) {
-        float4 p = *reinterpret_cast<const float4*>(mt.param + rowoff + col);
-        float pv[4] = {p.x, p.y, p.z, p.w};
-        float mv[4] = {0.f, 0.f, 0.f, 0.f};
-        if (h.has_momentum) {
-          float4 mo = *reinterpret_cast<const float4*>(mt.mom + rowoff + col);
-          mv[0] = mo.x; mv[1] = mo.y; mv[2] = mo.z; mv[3] = mo.w;
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) psgd_sgd_update(av[c], pv[c], &mv[c], h);
-        *reinterpret_cast<float4*>(mt.param + rowoff + col) = make_float4(pv[0], pv[1], pv[2], pv[3]);
-        if (h.has_momentum)
-          *reinterpret_cast<float4*>(mt.mom + rowoff + col) = make_float4(mv[0], mv[1], mv[2], mv[3]);
-      } else {
-        *reinterpret_cast<float4*>(mt.out + rowoff + col) = make_float4(av[0], av[1], av[2], av[3]);
-      }
+    for (int c = 0; c < 4; ++c) {
+      gv[c] -= accE[u][c];
+      av[c] = accA[u][c] * a.inv_world;
+      if (sgd) psgd_sgd_update(av[c], pv[c], &mv[c], h);
+    }
+    fin_store4<VEC>(mt.grad + rowoff, lane, t.cols, gv);
+    if (sgd) {
+      fin_store4<VEC>(mt.param + rowoff, lane, t.cols, pv);
+      if (mom) fin_store4<VEC>(mt.mom + rowoff, lane, t.cols, mv);
     } else {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int lc = lane + 32 * c;
-        if (lc >= t.cols) continue;
-        const long long off = rowoff + t.col0 + lc;
-        const float res = mt.grad[off] - accE[u][c];
-        const float av = accA[u][c] * a.inv_world;
-        mt.grad[off] = res;
-        if (a.fused_sgd) {
-          float p = mt.param[off];
-          float mo = h.has_momentum ? mt.mom[off] : 0.f;
-          psgd_sgd_update(av, p, &mo, h);
-          mt.param[off] = p;
-          if (h.has_momentum) mt.mom[off] = mo;
-        } else {
-          mt.out[off] = av;
-        }
-      }
+      fin_store4<VEC>(mt.out + rowoff, lane, t.cols, av);
     }
   }
   }  // row chunks
+}
+
+template <bool SAME>
+__global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs a) {
+  __shared__ __align__(16) float sLl[FIN_KC][FIN_ROWS];
+  __shared__ __align__(16) float sLs[FIN_KC][FIN_ROWS];
+  __shared__ __align__(16) float sRl[FIN_KC][FIN_COLS];
+  __shared__ __align__(16) float sRs[FIN_KC][FIN_COLS];
+  const PsgdTile whole = a.tiles[blockIdx.x];
+  const PsgdMat mt = a.mats[whole.mat];
+  if (whole.vec == 4) finalize_general_tile<4, SAME>(a, whole, mt, sLl, sLs, sRl, sRs);
+  else if (whole.vec == 2) finalize_general_tile<2, SAME>(a, whole, mt, sLl, sLs, sRl, sRs);
+  else finalize_general_tile<1, SAME>(a, whole, mt, sLl, sLs, sRl, sRs);
 }
 
 // Strip kernel (K = half-iterations x rank <= FIN_STRIP_KMAX): a CTA owns a strip of up to
@@ -204,11 +235,26 @@ __global__ void __launch_bounds__(FIN_THREADS) psgd_finalize_kernel(FinalizeArgs
 // loads (gradient, parameter, momentum) before its FMA loop so that their latency overlaps it.
 constexpr int FIN_STRIP_KMAX = 32;
 
+// Gather `n` consecutive words starting at slot index `base` of this epoch (sum over ranks in
+// rank order) and hand each to `put(i, value)`.
+template <class Put>
+__device__ __forceinline__ void fin_gather(const PsgdCommDev& c, int e1, long long base, int n, bool& ok, Put put) {
+  constexpr int NB = 4;
+  for (int i0 = threadIdx.x; i0 < n; i0 += NB * FIN_THREADS) {
+    int64_t idx[NB];
+    float v[NB];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) idx[j] = (i0 + j * FIN_THREADS < n) ? base + i0 + j * FIN_THREADS : -1;
+    psgd_comm_reduce_batch<NB>(c, e1, idx, NB, v, ok);
+#pragma unroll
+    for (int j = 0; j < NB; ++j)
+      if (i0 + j * FIN_THREADS < n) put(i0 + j * FIN_THREADS, v[j]);
+  }
+}
+
 template <int VEC, bool SAME>
-__global__ void __launch_bounds__(FIN_THREADS, 2) psgd_finalize_strip_kernel(FinalizeArgs a, int tile_rows) {
-  extern __shared__ __align__(16) float fin_smem[];
-  const PsgdTile t = a.tiles[blockIdx.x];
-  const PsgdMat mt = a.mats[t.mat];
+__device__ __forceinline__ void finalize_strip_tile(const FinalizeArgs& a, const PsgdTile& t, const PsgdMat& mt,
+                                                    int tile_rows, float* fin_smem) {
   const int r = mt.r, m = mt.m;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = a.nhist * r;
@@ -217,68 +263,79 @@ __global__ void __launch_bounds__(FIN_THREADS, 2) psgd_finalize_strip_kernel(Fin
   float* sRs = SAME ? sRl : sLl + K * tile_rows;
   float* sLs = SAME ? sLl : sRs + K * FIN_COLS;
 
+  const bool gather = !SAME && a.comm != nullptr;
+  int e1 = 0;
+  bool ok = true;
+  if (gather) e1 = *a.comm->epoch + 1;
   for (int h = 0; h < a.nhist; ++h) {
+    const bool last = gather && h == a.nhist - 1;
     {
       const long long base = mt.q_off + (long long)t.col0 * r;
       const float* gl = a.rloc[h] + base;
       const float* gs = a.rsum[h] + base;
+      const bool poll = last && !a.poll_left;
       for (int e = tid; e < t.cols * r; e += FIN_THREADS) {
         const int lc = e / r, j = e - lc * r;
-        // lane-major placement so that each lane's 4 columns are adjacent for the strided layout
-        const int pos = (VEC == 4) ? lc : ((lc & 31) * 4 + (lc >> 5));
+        const int pos = fin_panel_pos<VEC>(lc);
         sRl[(h * r + j) * FIN_COLS + pos] = gl[e];
-        if (!SAME) sRs[(h * r + j) * FIN_COLS + pos] = gs[e];
+        if (!SAME && !poll) sRs[(h * r + j) * FIN_COLS + pos] = gs[e];
+      }
+      if (poll) {
+        const bool writer = t.row0 == 0;
+        fin_gather(*a.comm, e1, base, t.cols * r, ok, [&](int e, float v) {
+          const int lc = e / r, j = e - lc * r;
+          sRs[(h * r + j) * FIN_COLS + fin_panel_pos<VEC>(lc)] = v;
+          if (writer) {
+            a.sum_out1[base + e] = v;
+            if (a.sum_out2) a.sum_out2[base + e] = v;
+          }
+        });
       }
     }
     {
       const long long base = mt.p_off + (long long)t.row0 * r;
       const float* gl = a.lloc[h] + base;
       const float* gs = a.lsum[h] + base;
+      const bool poll = last && a.poll_left;
       for (int e = tid; e < t.rows * r; e += FIN_THREADS) {
         const int lr = e / r, j = e - lr * r;
         sLl[(h * r + j) * tile_rows + lr] = gl[e];
-        if (!SAME) sLs[(h * r + j) * tile_rows + lr] = gs[e];
+        if (!SAME && !poll) sLs[(h * r + j) * tile_rows + lr] = gs[e];
+      }
+      if (poll) {
+        const bool writer = t.col0 == 0;
+        fin_gather(*a.comm, e1, base, t.rows * r, ok, [&](int e, float v) {
+          const int lr = e / r, j = e - lr * r;
+          sLs[(h * r + j) * tile_rows + lr] = v;
+          if (writer) {
+            a.sum_out1[base + e] = v;
+            if (a.sum_out2) a.sum_out2[base + e] = v;
+          }
+        });
       }
     }
   }
+  if (gather) psgd_comm_close_epoch(*a.comm, e1);  // (CTA barrier inside) this strip has read its words
   __syncthreads();
   const PsgdHyper hy = a.hyper[mt.hyper];
   const bool sgd = a.fused_sgd != 0;
   const bool mom = sgd && hy.has_momentum;
-  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
   for (int rc = 0; rc < t.rows; rc += FIN_ROWS) {
     // ---- global loads of this chunk first ----
-    float4 g4[4], p4[4], m4[4];
+    __align__(16) float g4[4][4], p4[4][4], m4[4][4];
     bool live[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int lr = rc + warp * 4 + u;
       const long long rowoff = (long long)(t.row0 + lr) * m + t.col0;
-      g4[u] = p4[u] = m4[u] = zero4;
-      if (VEC == 4) {
-        live[u] = lr < t.rows && lane * 4 < t.cols;
-        if (live[u]) {
-          g4[u] = *reinterpret_cast<const float4*>(mt.grad + rowoff + lane * 4);
-          if (sgd) p4[u] = *reinterpret_cast<const float4*>(mt.param + rowoff + lane * 4);
-          if (mom) m4[u] = *reinterpret_cast<const float4*>(mt.mom + rowoff + lane * 4);
-        }
-      } else {
-        live[u] = lr < t.rows;
-        if (live[u]) {
-          float* gv = reinterpret_cast<float*>(&g4[u]);
-          float* pv = reinterpret_cast<float*>(&p4[u]);
-          float* mv = reinterpret_cast<float*>(&m4[u]);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int lc = lane + 32 * c;
-            if (lc < t.cols) {
-              gv[c] = mt.grad[rowoff + lc];
-              if (sgd) pv[c] = mt.param[rowoff + lc];
-              if (mom) mv[c] = mt.mom[rowoff + lc];
-            }
-          }
-        }
+      for (int c4 = 0; c4 < 4; ++c4) g4[u][c4] = p4[u][c4] = m4[u][c4] = 0.f;
+      live[u] = lr < t.rows;
+      if (live[u]) {
+        fin_load4<VEC>(mt.grad + rowoff, lane, t.cols, g4[u]);
+        if (sgd) fin_load4<VEC>(mt.param + rowoff, lane, t.cols, p4[u]);
+        if (mom) fin_load4<VEC>(mt.mom + rowoff, lane, t.cols, m4[u]);
       }
     }
     // ---- rank-K update from the staged panels ----
@@ -286,7 +343,7 @@ __global__ void __launch_bounds__(FIN_THREADS, 2) psgd_finalize_strip_kernel(Fin
 #pragma unroll
     for (int u = 0; u < 4; ++u)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) accE[u][c] = accA[u][c] = 0.f;
+      for (int c4 = 0; c4 < 4; ++c4) accE[u][c4] = accA[u][c4] = 0.f;
 #pragma unroll 4
     for (int k = 0; k < K; ++k) {
       const float4 ll = *reinterpret_cast<const float4*>(sLl + k * tile_rows + rc + warp * 4);
@@ -298,9 +355,9 @@ __global__ void __launch_bounds__(FIN_THREADS, 2) psgd_finalize_strip_kernel(Fin
 #pragma unroll
       for (int u = 0; u < 4; ++u)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          accE[u][c] = fmaf(lv[u], rlv[c], accE[u][c]);
-          if (!SAME) accA[u][c] = fmaf(sv[u], rsv[c], accA[u][c]);
+        for (int c4 = 0; c4 < 4; ++c4) {
+          accE[u][c4] = fmaf(lv[u], rlv[c4], accE[u][c4]);
+          if (!SAME) accA[u][c4] = fmaf(sv[u], rsv[c4], accA[u][c4]);
         }
     }
     // ---- residual, mean update, optimizer ----
@@ -309,46 +366,38 @@ __global__ void __launch_bounds__(FIN_THREADS, 2) psgd_finalize_strip_kernel(Fin
       if (!live[u]) continue;
       const int lr = rc + warp * 4 + u;
       const long long rowoff = (long long)(t.row0 + lr) * m + t.col0;
-      float* gv = reinterpret_cast<float*>(&g4[u]);
-      float* pv = reinterpret_cast<float*>(&p4[u]);
-      float* mv = reinterpret_cast<float*>(&m4[u]);
-      float av[4];
+      __align__(16) float av[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        gv[c] -= accE[u][c];
-        av[c] = (SAME ? accE[u][c] : accA[u][c]) * a.inv_world;
-        if (sgd) psgd_sgd_update(av[c], pv[c], &mv[c], hy);
+      for (int c4 = 0; c4 < 4; ++c4) {
+        g4[u][c4] -= accE[u][c4];
+        av[c4] = (SAME ? accE[u][c4] : accA[u][c4]) * a.inv_world;
+        if (sgd) psgd_sgd_update(av[c4], p4[u][c4], &m4[u][c4], hy);
       }
-      if (VEC == 4) {
-        *reinterpret_cast<float4*>(mt.grad + rowoff + lane * 4) = g4[u];
-        if (sgd) {
-          *reinterpret_cast<float4*>(mt.param + rowoff + lane * 4) = p4[u];
-          if (mom) *reinterpret_cast<float4*>(mt.mom + rowoff + lane * 4) = m4[u];
-        } else {
-          *reinterpret_cast<float4*>(mt.out + rowoff + lane * 4) = make_float4(av[0], av[1], av[2], av[3]);
-        }
+      fin_store4<VEC>(mt.grad + rowoff, lane, t.cols, g4[u]);
+      if (sgd) {
+        fin_store4<VEC>(mt.param + rowoff, lane, t.cols, p4[u]);
+        if (mom) fin_store4<VEC>(mt.mom + rowoff, lane, t.cols, m4[u]);
       } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int lc = lane + 32 * c;
-          if (lc >= t.cols) continue;
-          mt.grad[rowoff + lc] = gv[c];
-          if (sgd) {
-            mt.param[rowoff + lc] = pv[c];
-            if (mom) mt.mom[rowoff + lc] = mv[c];
-          } else {
-            mt.out[rowoff + lc] = av[c];
-          }
-        }
+        fin_store4<VEC>(mt.out + rowoff, lane, t.cols, av);
       }
     }
   }
 }
 
-template <int VEC, bool SAME>
+template <bool SAME>
+__global__ void __launch_bounds__(FIN_THREADS, 2) psgd_finalize_strip_kernel(FinalizeArgs a, int tile_rows) {
+  extern __shared__ __align__(16) float fin_smem[];
+  const PsgdTile t = a.tiles[blockIdx.x];
+  const PsgdMat mt = a.mats[t.mat];
+  if (t.vec == 4) finalize_strip_tile<4, SAME>(a, t, mt, tile_rows, fin_smem);
+  else if (t.vec == 2) finalize_strip_tile<2, SAME>(a, t, mt, tile_rows, fin_smem);
+  else finalize_strip_tile<1, SAME>(a, t, mt, tile_rows, fin_smem);
+}
+
+template <bool SAME>
 static int finalize_strip_launch(const FinalizeArgs& a, int ntiles, int tile_rows, int kmax, cudaStream_t stream) {
   const size_t smem = (size_t)(SAME ? 1 : 2) * kmax * (FIN_COLS + tile_rows) * sizeof(float);
-  psgd_finalize_strip_kernel<VEC, SAME><<<ntiles, FIN_THREADS, smem, stream>>>(a, tile_rows);
+  psgd_finalize_strip_kernel<SAME><<<ntiles, FIN_THREADS, smem, stream>>>(a, tile_rows);
   return 0;
 }
 
@@ -361,20 +410,34 @@ PSGD_API int psgd_finalize_strip_rows(int kmax, int same) {
   return rows > 256 ? 256 : (rows < FIN_ROWS ? FIN_ROWS : rows);
 }
 
+static bool finalize_takes_strip(int nhist, int max_r, int tile_rows, bool same) {
+  const int kmax = nhist * max_r;
+  const size_t strip_smem = (size_t)(same ? 1 : 2) * kmax * (FIN_COLS + tile_rows) * sizeof(float);
+  return kmax <= FIN_STRIP_KMAX && strip_smem <= 48 * 1024;
+}
+
+// Whether psgd_finalize_launch runs the strip kernel for this configuration; only the strip kernel
+// can gather the last factor from the channel itself.
+PSGD_API int psgd_finalize_uses_strip(int nhist, int max_r, int tile_rows, int same) {
+  return finalize_takes_strip(nhist, max_r, tile_rows, same != 0) ? 1 : 0;
+}
+
 // tile_rows: height of the tallest tile in `tiles` (a multiple of 32); max_r: largest rank of a
 // matrix in `mats`. With nhist * max_r <= 32 and panels that fit shared memory the strip kernel
-// runs, else the general one.
-PSGD_API int psgd_finalize_launch(int vec4, const void* mats, const void* tiles, int ntiles, int tile_rows, int max_r,
+// runs, else the general one. Every tile carries its matrix's access width (`vec`).
+// comm / poll_left / sum_out1 / sum_out2: see FinalizeArgs (comm null: nothing is gathered).
+PSGD_API int psgd_finalize_launch(const void* mats, const void* tiles, int ntiles, int tile_rows, int max_r,
                                   const void* hyper, int nhist, const float* const* lloc, const float* const* rloc,
                                   const float* const* lsum, const float* const* rsum, float inv_world,
-                                  int fused_sgd, cudaStream_t stream) {
+                                  int fused_sgd, const void* comm, int poll_left, float* sum_out1, float* sum_out2,
+                                  cudaStream_t stream) {
   if (ntiles <= 0) return 0;
   if (tile_rows <= 0 || tile_rows % FIN_ROWS != 0 || max_r <= 0) {
     psgd_set_error("psgd_finalize_launch: tile_rows=%d must be a positive multiple of %d, max_r=%d positive", tile_rows, FIN_ROWS, max_r);
     return -1;
   }
-  if (nhist > PSGD_MAX_HIST) {
-    psgd_set_error("psgd_finalize_launch: %d half-iterations beyond the compiled maximum", nhist);
+  if (nhist > PSGD_MAX_HIST || nhist < 1) {
+    psgd_set_error("psgd_finalize_launch: %d half-iterations outside 1..%d", nhist, PSGD_MAX_HIST);
     return -1;
   }
   FinalizeArgs a;
@@ -390,27 +453,24 @@ PSGD_API int psgd_finalize_launch(int vec4, const void* mats, const void* tiles,
   }
   a.inv_world = inv_world;
   a.fused_sgd = fused_sgd;
+  a.comm = (const PsgdCommDev*)comm;
+  a.poll_left = poll_left;
+  a.sum_out1 = sum_out1;
+  a.sum_out2 = sum_out2;
   bool same = true;
   for (int i = 0; i < nhist; ++i) same = same && lloc[i] == lsum[i] && rloc[i] == rsum[i];
-  const int kmax = nhist * max_r;
-  const size_t strip_smem = (size_t)(same ? 1 : 2) * kmax * (FIN_COLS + tile_rows) * sizeof(float);
-  if (kmax <= FIN_STRIP_KMAX && strip_smem <= 48 * 1024) {
-    if (vec4) {
-      if (same) { if (finalize_strip_launch<4, true>(a, ntiles, tile_rows, kmax, stream)) return -1; }
-      else { if (finalize_strip_launch<4, false>(a, ntiles, tile_rows, kmax, stream)) return -1; }
-    } else {
-      if (same) { if (finalize_strip_launch<1, true>(a, ntiles, tile_rows, kmax, stream)) return -1; }
-      else { if (finalize_strip_launch<1, false>(a, ntiles, tile_rows, kmax, stream)) return -1; }
-    }
-    PSGD_CUDA_OK(cudaGetLastError());
-    return 0;
+  const bool strip = finalize_takes_strip(nhist, max_r, tile_rows, same);
+  if (comm != nullptr && (!strip || same || sum_out1 == nullptr)) {
+    psgd_set_error("psgd_finalize_launch: gathering from a channel needs the strip kernel, distinct summed factors and a destination");
+    return -1;
   }
-  if (vec4) {
-    if (same) psgd_finalize_kernel<4, true><<<ntiles, FIN_THREADS, 0, stream>>>(a);
-    else psgd_finalize_kernel<4, false><<<ntiles, FIN_THREADS, 0, stream>>>(a);
+  if (strip) {
+    const int kmax = nhist * max_r;
+    if (same) finalize_strip_launch<true>(a, ntiles, tile_rows, kmax, stream);
+    else finalize_strip_launch<false>(a, ntiles, tile_rows, kmax, stream);
   } else {
-    if (same) psgd_finalize_kernel<1, true><<<ntiles, FIN_THREADS, 0, stream>>>(a);
-    else psgd_finalize_kernel<1, false><<<ntiles, FIN_THREADS, 0, stream>>>(a);
+    if (same) psgd_finalize_kernel<true><<<ntiles, FIN_THREADS, 0, stream>>>(a);
+    else psgd_finalize_kernel<false><<<ntiles, FIN_THREADS, 0, stream>>>(a);
   }
   PSGD_CUDA_OK(cudaGetLastError());
   return 0;
@@ -434,6 +494,9 @@ struct FlatArgs {
              // 5: pack + push {value, epoch} words to every peer's slot (in-kernel all-reduce, part 1)
              // 6: poll the own slots, sum them in rank order -> out ; 7: same + SGD (part 2)
              // 8: accumulate (out += grad; no communication, `flat` unused)
+             // 9: mixed launch, every item names its own operation (`PsgdFlat::op`): 8, or 5 - the
+             //    residual fold of the compressed tensors and the pack + push of the uncompressed
+             //    ones leave in one launch
              // large buffers go two-shot (mode 0, then psgd_bulk_allreduce_launch on `flat`, which
              // is the data region of the arena, then one of):
              // 12: wait for the gathered chunks this block reads, then unpack ; 13: same + SGD
@@ -466,41 +529,42 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
   const PsgdHyper h = a.hyper[it.hyper];
   PsgdCommDev c;
   int e1 = 0;
-  const bool uses_comm = a.mode >= 5 && a.mode != 8;
+  const int mode = a.mode == 9 ? it.op : a.mode;
+  const bool uses_comm = mode >= 5 && mode != 8;
   if (uses_comm) {
     c = *a.comm;
     e1 = *c.epoch + 1;
   }
   bool ok = true;
-  if (a.mode >= 12)
+  if (mode >= 12)
     flat_wait_gathered(a, c, e1, it.flat_off + first, it.flat_off + min((long long)it.numel, first + (long long)FLAT_PER_BLOCK));
   for (int e = threadIdx.x; e < FLAT_PER_BLOCK; e += FLAT_THREADS) {
     const long long i = first + e;
     if (i >= it.numel) break;
     float g;
-    if (a.mode == 8) {
+    if (mode == 8) {
       it.out[i] += it.grad[i];
       continue;
-    } else if (a.mode == 0) {
+    } else if (mode == 0) {
       a.flat[it.flat_off + i] = it.grad[i] / a.divisor;
       it.grad[i] = 0.f;
       continue;
-    } else if (a.mode == 5) {
+    } else if (mode == 5) {
       const float v = it.grad[i] / a.divisor;
       it.grad[i] = 0.f;
       for (int p = 0; p < c.world; ++p) psgd_comm_store(psgd_comm_slot(c, p, e1, c.rank) + it.flat_off + i, v, e1);
       continue;
-    } else if (a.mode == 1 || a.mode == 2) {
+    } else if (mode == 1 || mode == 2) {
       g = a.flat[it.flat_off + i];
-    } else if (a.mode >= 12) {
+    } else if (mode >= 12) {
       g = __ldcg(a.flat + it.flat_off + i);  // written by peers: never through L1
-    } else if (a.mode >= 6) {
+    } else if (mode >= 6) {
       g = psgd_comm_reduce(c, e1, it.flat_off + i, ok);
     } else {
       g = it.grad[i] / a.divisor;
       it.grad[i] = 0.f;
     }
-    if (a.mode == 2 || a.mode == 4 || a.mode == 7 || a.mode == 13) {
+    if (mode == 2 || mode == 4 || mode == 7 || mode == 13) {
       float p = it.param[i];
       float mo = h.has_momentum ? it.mom[i] : 0.f;
       psgd_sgd_update(g, p, &mo, h);
@@ -510,7 +574,7 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
       it.out[i] = g;
     }
   }
-  if (uses_comm && a.mode >= 6) psgd_comm_close_epoch(c, e1);  // the last consumer CTA advances the channel
+  if (uses_comm && mode >= 6) psgd_comm_close_epoch(c, e1);  // the last consumer CTA advances the channel
 }
 
 // Streaming variant of the modes that move whole buffers (0-4, 12, 13): four elements per access.
@@ -519,7 +583,7 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
 template <int MODE>
 __device__ __forceinline__ void flat_one(const FlatArgs& a, const PsgdFlat& it, const PsgdHyper& h, long long i) {
   float g;
-  if (MODE == 8) {
+  if (MODE == 8 || MODE == 9) {
     it.out[i] += it.grad[i];
     return;
   } else if (MODE == 0) {
@@ -551,6 +615,18 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_vec_kernel(FlatArgs a)
   const long long first = a.block_first[blockIdx.x];
   const PsgdHyper h = a.hyper[it.hyper];
   const long long left = min((long long)it.numel - first, (long long)FLAT_PER_BLOCK);
+  if (MODE == 9 && it.op == 5) {
+    // pack + push of an uncompressed tensor: element-wise tagged words (see psgd_flat_kernel)
+    const PsgdCommDev& cc = *a.comm;
+    const int ep = *cc.epoch + 1;
+    for (int e = threadIdx.x; e < left; e += FLAT_THREADS) {
+      const long long i = first + e;
+      const float v = it.grad[i] / a.divisor;
+      it.grad[i] = 0.f;
+      for (int p = 0; p < cc.world; ++p) psgd_comm_store(psgd_comm_slot(cc, p, ep, cc.rank) + it.flat_off + i, v, ep);
+    }
+    return;
+  }
   PsgdCommDev c;
   int e1 = 0;
   if (MODE >= 12) {
@@ -572,7 +648,7 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_vec_kernel(FlatArgs a)
     float4 g;
     float4* grad4 = (float4*)(it.grad + i);
     float4* flat4 = (float4*)(a.flat + it.flat_off + i);
-    if (MODE == 8) {
+    if (MODE == 8 || MODE == 9) {
       const float4 add = *grad4;
       float4* o4 = (float4*)(it.out + i);
       float4 o = *o4;
@@ -629,7 +705,8 @@ static void flat_vec_launch(const FlatArgs& a, int nblocks, cudaStream_t stream)
 }
 
 // vec != 0 promises 16-byte aligned grad / param / mom / out pointers and flat offsets that are
-// multiples of four floats; modes 5-7 (flag-in-data words) always run element-wise.
+// multiples of four floats; modes 5-7 (flag-in-data words) always run element-wise, and so do the
+// op-5 items of a mixed launch (mode 9), whose pointers need no alignment.
 PSGD_API int psgd_flat_launch(int mode, int vec, const void* items, const int* block_item, const int* block_first,
                               int nblocks, const void* hyper, float* flat, float divisor, const void* comm,
                               long long n_pad, cudaStream_t stream) {
@@ -638,7 +715,7 @@ PSGD_API int psgd_flat_launch(int mode, int vec, const void* items, const int* b
     psgd_set_error("psgd_flat_launch: mode %d needs a communication channel", mode);
     return -1;
   }
-  if (!((mode >= 0 && mode <= 8) || mode == 12 || mode == 13)) {
+  if (!((mode >= 0 && mode <= 9) || mode == 12 || mode == 13)) {
     psgd_set_error("psgd_flat_launch: unknown mode %d", mode);
     return -1;
   }
@@ -660,6 +737,7 @@ PSGD_API int psgd_flat_launch(int mode, int vec, const void* items, const int* b
       case 3: flat_vec_launch<3>(a, nblocks, stream); break;
       case 4: flat_vec_launch<4>(a, nblocks, stream); break;
       case 8: flat_vec_launch<8>(a, nblocks, stream); break;
+      case 9: flat_vec_launch<9>(a, nblocks, stream); break;
       case 12: flat_vec_launch<12>(a, nblocks, stream); break;
       default: flat_vec_launch<13>(a, nblocks, stream); break;
     }

@@ -58,7 +58,11 @@ __device__ __forceinline__ bool ft_wait(uint64_t* bar, uint32_t parity, volatile
     if (*abort_flag) return false;
     if (psgd_globaltimer_ns() - t0 > FT_WAIT_LIMIT_NS) {
       *abort_flag = 1;
-      if (status) atomicExch(status, (int)PSGD_TIMEOUT_MBARRIER);
+      if (status) {
+        // plain store: the word may live in mapped pinned host memory, which the host reads
+        *((volatile int*)status) = (int)PSGD_TIMEOUT_MBARRIER;
+        __threadfence_system();
+      }
       return false;
     }
   }

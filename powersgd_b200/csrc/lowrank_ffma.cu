@@ -11,7 +11,9 @@
 //
 // At rank r the product does 2r flops per 4 bytes of M, so for r <= 8 float32 FMAs keep up
 // with HBM and this path is bandwidth-bound; it is also the path for matrices whose row
-// pitch is not a multiple of 16 bytes (27, 650 floats), which TMA cannot address.
+// pitch is not a multiple of 16 bytes (27, 650 floats), which TMA cannot address. Every tile
+// names the widest global access its matrix allows (16, 8 or 4 bytes: `PsgdTile::vec`), so one
+// launch serves all of them.
 //
 // Tiles that cover the same output rows (NT: row blocks of one column block; NN: column
 // blocks of one row block) write partial sums to a scratch arena; the tile that arrives last
@@ -29,6 +31,7 @@ struct GemmArgs {
   const PsgdTile* tiles;
   const float* in;    // orthonormal factor: P-shaped for NT, Q-shaped for NN
   float* out;         // fresh local factor: Q-shaped for NT, P-shaped for NN
+  float* out2;        // optional second copy of it (single worker: the warm-start buffer) or null
   int ncorr;
   const float* corr_fac[PSGD_MAX_HIST];  // earlier local factors on the OUTPUT side
   const float* corr_c[PSGD_MAX_HIST];    // [mat][r*r] cross products
@@ -42,17 +45,44 @@ struct GemmArgs {
 template <int RT>
 __host__ __device__ constexpr int nt_max_rows() { return RT <= 16 ? NT_MAX_ROWS : NT_MAX_ROWS / 2; }
 
+// A lane owns 4 of the 128 columns of a column block; which ones depends on the access width:
+// 4 adjacent (one 16-byte load), 2 + 2 adjacent (two 8-byte loads, 64 columns apart) or 4
+// columns 32 apart (scalar loads). Every variant keeps a warp's accesses contiguous.
+template <int VEC>
+__device__ __forceinline__ int lane_col(int lane, int c) {
+  if (VEC == 4) return 4 * lane + c;
+  if (VEC == 2) return (c < 2) ? 2 * lane + c : 64 + 2 * lane + (c - 2);
+  return lane + 32 * c;
+}
+
+// v[0..3] = the lane's four columns of the row at `rowp` (column block starting at c0, valid up
+// to cend); zero where the row or the column does not exist.
+template <int VEC>
+__device__ __forceinline__ void load_lane_cols(const float* __restrict__ rowp, int c0, int cend, int lane, bool rok,
+                                               float* v) {
+  if (VEC == 4) {
+    float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (rok && c0 + 4 * lane < cend) q = __ldg(reinterpret_cast<const float4*>(rowp + c0 + 4 * lane));
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  } else if (VEC == 2) {
+    float2 q0 = make_float2(0.f, 0.f), q1 = make_float2(0.f, 0.f);
+    if (rok && c0 + 2 * lane < cend) q0 = __ldg(reinterpret_cast<const float2*>(rowp + c0 + 2 * lane));
+    if (rok && c0 + 64 + 2 * lane < cend) q1 = __ldg(reinterpret_cast<const float2*>(rowp + c0 + 64 + 2 * lane));
+    v[0] = q0.x; v[1] = q0.y; v[2] = q1.x; v[3] = q1.y;
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) v[c] = (rok && c0 + lane + 32 * c < cend) ? __ldg(rowp + c0 + lane + 32 * c) : 0.f;
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // NT: each lane owns 4 columns, each warp strides over the tile's rows.
 // ------------------------------------------------------------------------------------------
 template <int RT, int VEC>
-__global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) {
-  const PsgdTile t = a.tiles[blockIdx.x];
-  const PsgdMat mt = a.mats[t.mat];
+__device__ __forceinline__ void gemm_nt_tile(const GemmArgs& a, const PsgdTile& t, const PsgdMat& mt, float* smem) {
   const int r = mt.r, m = mt.m;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-  extern __shared__ float smem[];
   float* sP = smem;                        // [rows][RT]
   float* sSum = smem + nt_max_rows<RT>() * RT;   // [128][RT]
   __shared__ int sLast;
@@ -72,13 +102,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) 
     for (int k = 0; k < RT; ++k) acc[c][k] = 0.f;
 
   const float* __restrict__ M = mt.grad;
-  int colv[4];
-  bool colok[4];
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    colv[c] = t.col0 + (VEC == 4 ? 4 * lane + c : lane + 32 * c);
-    colok[c] = colv[c] < t.col0 + t.cols;
-  }
+  const int cend = t.col0 + t.cols;
 
   for (int i0 = warp; i0 < t.rows; i0 += GEMM_WARPS * 4) {
     float v[4][4];
@@ -86,15 +110,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) 
     for (int u = 0; u < 4; ++u) {
       const int i = i0 + u * GEMM_WARPS;
       const bool rok = i < t.rows;
-      const float* rowp = M + (long long)(t.row0 + (rok ? i : 0)) * m;
-      if (VEC == 4) {
-        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (rok && colok[0]) q = __ldg(reinterpret_cast<const float4*>(rowp + colv[0]));
-        v[u][0] = q.x; v[u][1] = q.y; v[u][2] = q.z; v[u][3] = q.w;
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) v[u][c] = (rok && colok[c]) ? __ldg(rowp + colv[c]) : 0.f;
-      }
+      load_lane_cols<VEC>(M + (long long)(t.row0 + (rok ? i : 0)) * m, t.col0, cend, lane, rok, v[u]);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -116,7 +132,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) 
     if (warp == w) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const int lc = (VEC == 4 ? 4 * lane + c : lane + 32 * c);
+        const int lc = lane_col<VEC>(lane, c);
 #pragma unroll
         for (int k = 0; k < RT; ++k) {
           if (w == 0) sSum[lc * RT + k] = acc[c][k];
@@ -172,22 +188,29 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) 
       s -= d;
     }
     qout[(long long)col * r + k] = s;
+    if (a.out2) a.out2[mt.q_off + (long long)col * r + k] = s;
     for (int p = 0; p < npush; ++p) psgd_comm_store(push[p] + (long long)col * r + k, s, e1);
   }
+}
+
+template <int RT>
+__global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nt_kernel(GemmArgs a) {
+  extern __shared__ float smem[];
+  const PsgdTile t = a.tiles[blockIdx.x];
+  const PsgdMat mt = a.mats[t.mat];
+  if (t.vec == 4) gemm_nt_tile<RT, 4>(a, t, mt, smem);
+  else if (t.vec == 2) gemm_nt_tile<RT, 2>(a, t, mt, smem);
+  else gemm_nt_tile<RT, 1>(a, t, mt, smem);
 }
 
 // ------------------------------------------------------------------------------------------
 // NN: each warp owns RPW rows; lanes stride across the columns and shuffle-reduce at the end.
 // ------------------------------------------------------------------------------------------
 template <int RT, int VEC, int RPW>
-__global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nn_kernel(GemmArgs a) {
-  const PsgdTile t = a.tiles[blockIdx.x];
-  const PsgdMat mt = a.mats[t.mat];
+__device__ __forceinline__ void gemm_nn_tile(const GemmArgs& a, const PsgdTile& t, const PsgdMat& mt, float* sSum) {
   const int r = mt.r, m = mt.m;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int TILE_ROWS = GEMM_WARPS * RPW;
-
-  __shared__ float sSum[TILE_ROWS * RT];
   __shared__ int sLast;
 
   const float* __restrict__ M = mt.grad;
@@ -210,29 +233,14 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nn_kernel(GemmArgs a) 
 
   const int cend = t.col0 + t.cols;
   for (int c0 = t.col0; c0 < cend; c0 += NN_CHUNK_COLS) {
-    int colv[4];
-    bool colok[4];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      colv[c] = c0 + (VEC == 4 ? 4 * lane + c : lane + 32 * c);
-      colok[c] = colv[c] < cend;
-    }
     float v[RPW][4];
 #pragma unroll
-    for (int u = 0; u < RPW; ++u) {
-      if (VEC == 4) {
-        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (rok[u] && colok[0]) q = __ldg(reinterpret_cast<const float4*>(rowp[u] + colv[0]));
-        v[u][0] = q.x; v[u][1] = q.y; v[u][2] = q.z; v[u][3] = q.w;
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) v[u][c] = (rok[u] && colok[c]) ? __ldg(rowp[u] + colv[c]) : 0.f;
-      }
-    }
+    for (int u = 0; u < RPW; ++u) load_lane_cols<VEC>(rowp[u], c0, cend, lane, rok[u], v[u]);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      if (colok[c]) {
-        const float* qr = qin + (long long)colv[c] * r;
+      const int col = c0 + lane_col<VEC>(lane, c);
+      if (col < cend) {
+        const float* qr = qin + (long long)col * r;
 #pragma unroll
         for (int k = 0; k < RT; ++k) {
           const float qk = (k < r) ? __ldg(qr + k) : 0.f;
@@ -296,20 +304,32 @@ __global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nn_kernel(GemmArgs a) 
       s -= d;
     }
     pout[(long long)row * r + k] = s;
+    if (a.out2) a.out2[mt.p_off + (long long)row * r + k] = s;
     for (int p = 0; p < npush; ++p) psgd_comm_store(push[p] + (long long)row * r + k, s, e1);
   }
+}
+
+template <int RT, int RPW>
+__global__ void __launch_bounds__(GEMM_THREADS) psgd_gemm_nn_kernel(GemmArgs a) {
+  __shared__ float sSum[GEMM_WARPS * RPW * RT];
+  const PsgdTile t = a.tiles[blockIdx.x];
+  const PsgdMat mt = a.mats[t.mat];
+  if (t.vec == 4) gemm_nn_tile<RT, 4, RPW>(a, t, mt, sSum);
+  else if (t.vec == 2) gemm_nn_tile<RT, 2, RPW>(a, t, mt, sSum);
+  else gemm_nn_tile<RT, 1, RPW>(a, t, mt, sSum);
 }
 
 // ------------------------------------------------------------------------------------------
 // Host launchers
 // ------------------------------------------------------------------------------------------
-static void fill_args(GemmArgs& a, const void* mats, const void* tiles, const float* in, float* out, int ncorr,
-                      const float* const* corr_fac, const float* const* corr_c, float* partial, int* tickets,
-                      const void* comm) {
+static void fill_args(GemmArgs& a, const void* mats, const void* tiles, const float* in, float* out, float* out2,
+                      int ncorr, const float* const* corr_fac, const float* const* corr_c, float* partial,
+                      int* tickets, const void* comm) {
   a.mats = (const PsgdMat*)mats;
   a.tiles = (const PsgdTile*)tiles;
   a.in = in;
   a.out = out;
+  a.out2 = out2;
   a.ncorr = ncorr;
   for (int i = 0; i < PSGD_MAX_HIST; ++i) {
     a.corr_fac[i] = i < ncorr ? corr_fac[i] : nullptr;
@@ -320,35 +340,34 @@ static void fill_args(GemmArgs& a, const void* mats, const void* tiles, const fl
   a.comm = (const PsgdCommDev*)comm;
 }
 
-template <int RT, int VEC>
+template <int RT>
 static int launch_nt(const GemmArgs& a, int ntiles, cudaStream_t stream) {
   const size_t smem = (size_t)(nt_max_rows<RT>() * RT + NT_TILE_COLS * RT) * sizeof(float);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
-    PSGD_CUDA_OK(cudaFuncSetAttribute(psgd_gemm_nt_kernel<RT, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)smem));
+    PSGD_CUDA_OK(cudaFuncSetAttribute(psgd_gemm_nt_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  psgd_gemm_nt_kernel<RT, VEC><<<ntiles, GEMM_THREADS, smem, stream>>>(a);
+  psgd_gemm_nt_kernel<RT><<<ntiles, GEMM_THREADS, smem, stream>>>(a);
   PSGD_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
-template <int RT, int VEC>
+template <int RT>
 static int launch_nn(const GemmArgs& a, int ntiles, cudaStream_t stream) {
   constexpr int RPW = RT <= 8 ? 4 : (RT == 16 ? 2 : 1);
-  psgd_gemm_nn_kernel<RT, VEC, RPW><<<ntiles, GEMM_THREADS, 0, stream>>>(a);
+  psgd_gemm_nn_kernel<RT, RPW><<<ntiles, GEMM_THREADS, 0, stream>>>(a);
   PSGD_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
-#define PSGD_DISPATCH_RT(FN, VECV)                                   \
-  if (max_r <= 1) return FN<1, VECV>(a, ntiles, stream);             \
-  if (max_r <= 2) return FN<2, VECV>(a, ntiles, stream);             \
-  if (max_r <= 4) return FN<4, VECV>(a, ntiles, stream);             \
-  if (max_r <= 8) return FN<8, VECV>(a, ntiles, stream);             \
-  if (max_r <= 16) return FN<16, VECV>(a, ntiles, stream);           \
-  return FN<32, VECV>(a, ntiles, stream);
+#define PSGD_DISPATCH_RT(FN)                                   \
+  if (max_r <= 1) return FN<1>(a, ntiles, stream);             \
+  if (max_r <= 2) return FN<2>(a, ntiles, stream);             \
+  if (max_r <= 4) return FN<4>(a, ntiles, stream);             \
+  if (max_r <= 8) return FN<8>(a, ntiles, stream);             \
+  if (max_r <= 16) return FN<16>(a, ntiles, stream);           \
+  return FN<32>(a, ntiles, stream);
 
 // Rows handled by one NN tile for the template rank that `max_r` selects (the planner needs it).
 PSGD_API int psgd_gemm_nn_tile_rows(int max_r) {
@@ -360,10 +379,11 @@ PSGD_API int psgd_gemm_template_rank(int max_r) {
   return max_r <= 1 ? 1 : max_r <= 2 ? 2 : max_r <= 4 ? 4 : max_r <= 8 ? 8 : max_r <= 16 ? 16 : 32;
 }
 
-// `transposed` != 0: NT (Q = M^T P); else NN (P = M Q). `vec4` != 0 only if every matrix of the
-// tile list has a 16-byte aligned base and m % 4 == 0.
-PSGD_API int psgd_gemm_ffma_launch(int transposed, int vec4, int max_r, const void* mats, const void* tiles,
-                                   int ntiles, const float* in, float* out, int ncorr,
+// `transposed` != 0: NT (Q = M^T P); else NN (P = M Q). Every tile carries the access width of
+// its matrix (`vec`: 4 needs a 16-byte aligned base and m % 4 == 0; 2 an 8-byte aligned base and
+// an even m). `out2`, when not null, receives a second copy of the fresh factor.
+PSGD_API int psgd_gemm_ffma_launch(int transposed, int max_r, const void* mats, const void* tiles, int ntiles,
+                                   const float* in, float* out, float* out2, int ncorr,
                                    const float* const* corr_fac, const float* const* corr_c, float* partial,
                                    int* tickets, const void* comm, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
@@ -372,10 +392,7 @@ PSGD_API int psgd_gemm_ffma_launch(int transposed, int vec4, int max_r, const vo
     return -1;
   }
   GemmArgs a;
-  fill_args(a, mats, tiles, in, out, ncorr, corr_fac, corr_c, partial, tickets, comm);
-  if (transposed) {
-    if (vec4) { PSGD_DISPATCH_RT(launch_nt, 4) } else { PSGD_DISPATCH_RT(launch_nt, 1) }
-  } else {
-    if (vec4) { PSGD_DISPATCH_RT(launch_nn, 4) } else { PSGD_DISPATCH_RT(launch_nn, 1) }
-  }
+  fill_args(a, mats, tiles, in, out, out2, ncorr, corr_fac, corr_c, partial, tickets, comm);
+  if (transposed) { PSGD_DISPATCH_RT(launch_nt) }
+  PSGD_DISPATCH_RT(launch_nn)
 }

@@ -63,7 +63,8 @@ struct TcArgs {
   float* partial;
   int* tickets;
   const PsgdCommDev* comm;
-  int* status;               // device word, set on a wait that ran out
+  float* out2;               // optional second copy of the fresh factor or null
+  int* status;               // word (device or mapped host memory) set on a wait that ran out
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -97,7 +98,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (*abort_flag) return false;
     if (psgd_globaltimer_ns() - t0 > TC_WAIT_LIMIT_NS) {
       *abort_flag = 1;
-      if (status) atomicExch(status, (int)PSGD_TIMEOUT_MBARRIER);
+      if (status) {
+        // plain store: the word may live in mapped pinned host memory, which the host reads
+        *((volatile int*)status) = (int)PSGD_TIMEOUT_MBARRIER;
+        __threadfence_system();
+      }
       return false;
     }
   }
@@ -430,6 +435,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) psgd_gemm_tc_kernel(const __gri
       s -= dsum;
     }
     fout[row * r + k] = s;
+    if (a.out2) a.out2[out_off + row * r + k] = s;
     for (int p = 0; p < npush; ++p) psgd_comm_store(push[p] + row * r + k, s, e1);
   }
 }
@@ -514,7 +520,7 @@ PSGD_API int psgd_tma_encode_matrix(void* out, const float* base, int n, int m) 
 // Same contract as psgd_gemm_ffma_launch; `maps` is a device array of tensor maps indexed like
 // `mats`; `split` selects split-precision TF32 (FP32-accurate) or plain TF32.
 PSGD_API int psgd_gemm_tc_launch(int transposed, int split, int max_r, const void* mats, const void* tiles, int ntiles,
-                                 const void* maps, const float* in, float* out, int ncorr,
+                                 const void* maps, const float* in, float* out, float* out2, int ncorr,
                                  const float* const* corr_fac, const float* const* corr_c, float* partial,
                                  int* tickets, const void* comm, int* status, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
@@ -528,6 +534,7 @@ PSGD_API int psgd_gemm_tc_launch(int transposed, int split, int max_r, const voi
   a.maps = (const CUtensorMap*)maps;
   a.in = in;
   a.out = out;
+  a.out2 = out2;
   a.ncorr = ncorr;
   for (int i = 0; i < PSGD_MAX_HIST; ++i) {
     a.corr_fac[i] = i < ncorr ? corr_fac[i] : nullptr;

@@ -25,7 +25,13 @@
 // kernels use to deflate algebraically. The second launch applies R^-1 to every row chunk. A long
 // factor (an embedding with 50 000 rows, rank 16) thus takes microseconds instead of the
 // hundreds that one CTA per unit needed.
-#include "psgd_common.cuh"
+//
+// Multi-GPU: the factor to orthonormalise is the SUM over workers of what the previous product
+// launch pushed into this rank's slot arena. The first launch is then also the consumer of that
+// in-kernel all-reduce (powersgd/powersgd.py:205-209 in the reference is a blocking library
+// call): while staging its chunk every CTA polls the tagged words of the W slots, adds them in
+// rank order, and writes the sum to the factor buffer and to the copy the decompression reads.
+#include "psgd_comm.cuh"
 
 typedef struct {
   int32_t x_off;      // float offset of the unit inside the factor buffer
@@ -57,6 +63,8 @@ struct OrthArgs {
   double* rinv;                      // scratch: [unit][RT*RT]  R^-1 (rank 1: [0] = the divisor)
   int* dead;                         // scratch: [unit][RT]     column status (see sDead)
   int* tickets;                      // [unit], zero between launches
+  const PsgdCommDev* comm;           // not null: x is first gathered from the channel's slots (see above)
+  float* sum_out;                    // with comm: second destination of the gathered sum (laid out like x)
 };
 
 constexpr int ORTH_THREADS = 256;
@@ -127,9 +135,40 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_gram_kernel(OrthArgs a
   // ---- partial sums of this chunk ---------------------------------------------------------
   const int stride = 1 + a.nprev;
   double* my_part = a.part + (long long)blockIdx.x * stride * NP;
-  for (int e = tid; e < ch.rows * RT; e += ORTH_THREADS) {
-    const int row = e / RT, c = e % RT;
-    sx[e] = c < r ? (double)x[(long long)(ch.row0 + row) * r + c] : 0.0;
+  if (a.comm != nullptr) {
+    // gather: this chunk is a contiguous run of rows * r words in every slot
+    const PsgdCommDev& c = *a.comm;
+    const int e1 = *c.epoch + 1;
+    const long long base = (long long)u.x_off + (long long)ch.row0 * r;
+    float* __restrict__ xw = a.x + base;
+    float* __restrict__ sw = a.sum_out + base;
+    const int n = ch.rows * r;
+    for (int e = tid; e < ch.rows * RT; e += ORTH_THREADS)
+      if (e % RT >= r) sx[e] = 0.0;
+    bool ok = true;
+    constexpr int NB = 4;
+    for (int i0 = tid; i0 < n; i0 += NB * ORTH_THREADS) {
+      int64_t idx[NB];
+      float v[NB];
+#pragma unroll
+      for (int j = 0; j < NB; ++j) idx[j] = (i0 + j * ORTH_THREADS < n) ? base + i0 + j * ORTH_THREADS : -1;
+      psgd_comm_reduce_batch<NB>(c, e1, idx, NB, v, ok);
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        const int i = i0 + j * ORTH_THREADS;
+        if (i < n) {
+          xw[i] = v[j];
+          sw[i] = v[j];
+          sx[(i / r) * RT + i % r] = (double)v[j];
+        }
+      }
+    }
+    psgd_comm_close_epoch(c, e1);  // (CTA barrier inside) every word of this chunk has been read
+  } else {
+    for (int e = tid; e < ch.rows * RT; e += ORTH_THREADS) {
+      const int row = e / RT, c = e % RT;
+      sx[e] = c < r ? (double)x[(long long)(ch.row0 + row) * r + c] : 0.0;
+    }
   }
   __syncthreads();
   chunk_pairs<RT>(sx, sx, ch.rows, red, my_part, tid);
@@ -362,9 +401,11 @@ PSGD_API int psgd_orth_part_doubles(int max_r, int nprev) {
 // units / chunks: device tables; all units of one call share the template rank RT >= max r.
 // part: nchunks * psgd_orth_part_doubles(max_r, nprev) doubles; rinv: nunits * RT*RT doubles;
 // dead: nunits * RT ints; tickets: nunits ints, zero (the kernel leaves them zero).
+// comm / sum_out: see OrthArgs (null for a single worker or when x already holds the factor).
 PSGD_API int psgd_orth_launch(const void* units, int nunits, const void* chunks, int nchunks, int max_r, float* x,
                               float* copy_to, int nprev, const float* const* prev, float* const* cmat,
-                              double* part, double* rinv, int* dead, int* tickets, cudaStream_t stream) {
+                              double* part, double* rinv, int* dead, int* tickets, const void* comm,
+                              float* sum_out, cudaStream_t stream) {
   if (nunits <= 0 || nchunks <= 0) return 0;
   if (max_r > PSGD_MAX_RANK || nprev > PSGD_MAX_HIST) {
     psgd_set_error("psgd_orth_launch: rank %d or history %d beyond the compiled maximum", max_r, nprev);
@@ -384,6 +425,12 @@ PSGD_API int psgd_orth_launch(const void* units, int nunits, const void* chunks,
   a.rinv = rinv;
   a.dead = dead;
   a.tickets = tickets;
+  a.comm = (const PsgdCommDev*)comm;
+  a.sum_out = sum_out;
+  if (comm != nullptr && sum_out == nullptr) {
+    psgd_set_error("psgd_orth_launch: a channel was given without a destination for the gathered sum");
+    return -1;
+  }
   switch (psgd_orth_template_rank(max_r)) {
     case 1: orth_launch_rt<1>(a, nchunks, stream); break;
     case 2: orth_launch_rt<2>(a, nchunks, stream); break;

@@ -77,6 +77,30 @@ __device__ __forceinline__ float psgd_comm_reduce(const PsgdCommDev& c, int epoc
   return s;
 }
 
+// Sum over ranks, in rank order, of N elements (indices idx[j], j < n <= N; idx[j] < 0 skips) of
+// this epoch's slots of the own arena. All N peeks of one rank's slot are issued before any tag
+// is looked at, so a thread with several elements pays one load latency per rank, not per word.
+template <int N>
+__device__ __forceinline__ void psgd_comm_reduce_batch(const PsgdCommDev& c, int epoch, const int64_t* idx, int n,
+                                                       float* out, bool& ok) {
+#pragma unroll
+  for (int j = 0; j < N; ++j) out[j] = 0.f;
+  for (int r = 0; r < c.world; ++r) {
+    const uint2* slot = psgd_comm_slot(c, c.rank, epoch, r);
+    uint2 w[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+      if (j < n && idx[j] >= 0) w[j] = psgd_comm_peek(slot + idx[j]);
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      if (j < n && idx[j] >= 0) {
+        const float v = ((int)w[j].y == epoch) ? __uint_as_float(w[j].x) : psgd_comm_load(c, slot + idx[j], epoch, ok);
+        out[j] += v;
+      }
+    }
+  }
+}
+
 // Consumer launches close the epoch: the CTA that arrives last advances the channel.
 __device__ __forceinline__ void psgd_comm_close_epoch(const PsgdCommDev& c, int epoch) {
   __syncthreads();

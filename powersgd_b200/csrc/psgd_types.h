@@ -30,7 +30,9 @@ typedef struct {
   int32_t split, nsplit;   // this tile's position among the tiles whose partial sums are added
   int32_t ticket;          // index of the arrival counter shared by those tiles
   int32_t slot0;           // first partial-sum slot of that set (slot = slot0 + split)
-  int32_t pad[3];
+  int32_t vec;             // floats per global access the matrix allows: 4 (16-byte aligned rows),
+                           // 2 (8-byte aligned rows, e.g. a row pitch of 650 floats) or 1
+  int32_t pad[2];
 } PsgdTile;  // 48 bytes
 
 // SGD hyper-parameters of one parameter group (read on the device every step, so the
@@ -51,5 +53,6 @@ typedef struct {
   int64_t numel;
   int64_t flat_off;  // offset inside the flat communication buffer
   int32_t hyper;
-  int32_t pad[3];
+  int32_t op;        // per-item operation of a mixed launch (psgd_flat_launch mode 9): 8 or 5
+  int32_t pad[2];
 } PsgdFlat;  // 64 bytes

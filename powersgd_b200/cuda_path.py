@@ -3,9 +3,10 @@
 Per optimizer step the reference issues several hundred small PyTorch ops
 (powersgd/powersgd.py:146-235). Here a step is, for T half-iterations:
 
-    T x [ orthonormalise (2 launches) -> grouped product (1-2 launches; multi-GPU: its epilogue
-          pushes the fresh factor to every peer) -> sum of the peers' slots (1 small launch) ]
-      ->  decompress + error feedback (+ SGD) (1-2 launches)
+    T x [ orthonormalise (2 launches; multi-GPU: the first one also gathers the factor the previous
+          product pushed, i.e. it is the consumer of the in-kernel all-reduce)
+          -> grouped product (1 launch; multi-GPU: its epilogue pushes the fresh factor to every peer) ]
+      ->  decompress + error feedback (+ SGD) (1 launch; multi-GPU: gathers the last factor itself)
 
 over ALL shape groups at once. The gradient matrices are addressed in place through a
 pointer table (no `torch.stack`, no un-batching copies), the deflation between half-iterations
@@ -86,12 +87,30 @@ def _to_device(array: np.ndarray, device: torch.device) -> torch.Tensor:
     out._psgd_pinned_src = pinned
     if torch.cuda.is_current_stream_capturing():
         # the recorded copy node reads `pinned` and writes `out` on every replay: both must
-        # outlive whatever later rebinding drops them from their owner
-        _CAPTURED_TABLES.append((out, pinned))
+        # outlive whatever later rebinding drops them from their owner, i.e. live as long as the
+        # graph does. Inside a `capture_scope` the graph's owner keeps them; a capture made
+        # without one parks them here for the life of the process.
+        (_capture_keep if _capture_keep is not None else _CAPTURED_TABLES).append((out, pinned))
     return out
 
 
 _CAPTURED_TABLES: list = []
+_capture_keep: Optional[list] = None
+
+
+class capture_scope:
+    """`with capture_scope() as keep:` around a CUDA-graph capture collects the descriptor tables
+    uploaded during it in `keep`; store `keep` next to the graph and drop both together."""
+
+    def __enter__(self) -> list:
+        global _capture_keep
+        self._outer = _capture_keep
+        _capture_keep = []
+        return _capture_keep
+
+    def __exit__(self, *exc):
+        global _capture_keep
+        _capture_keep = self._outer
 
 
 def _split_even(total: int, max_chunk: int, multiple: int) -> List[Tuple[int, int]]:
@@ -131,16 +150,16 @@ class TilePlan:
         self.fin_tc_ok = False  # set by the compressor: (half-iterations x rank) fits the tensor-core finalize
         self.fin_rows = 32      # set by the compressor: height of a finalize strip (multiple of 32)
 
-    def build(self, vec_flags: Sequence[bool], tc_flags: Optional[Sequence[bool]] = None):
-        """Tile arrays split by vector width (CUDA-core kernels: keys 4 and 1) and, for the
-        matrices flagged in `tc_flags`, tensor-core tiles (key "tc")."""
-        nt = {4: [], 1: [], "tc": []}
-        nn = {4: [], 1: [], "tc": []}
-        fin = {4: [], 1: [], "tc": []}
+    def build(self, vec_widths: Sequence[int], tc_flags: Optional[Sequence[bool]] = None):
+        """Tile arrays for the CUDA-core kernels (key "f"; every tile carries the access width of
+        its matrix: 4, 2 or 1 floats) and, for the matrices flagged in `tc_flags`, tensor-core
+        tiles (key "tc")."""
+        nt = {"f": [], "tc": []}
+        nn = {"f": [], "tc": []}
+        fin = {"f": [], "tc": []}
         ticket = 0
         nt_slots = nn_slots = tc_slots = 0
         tc_flags = tc_flags or [False] * len(self.mats)
-        n_tc_elems = sum(self.plan.groups[gi].n * self.plan.groups[gi].m for (gi, _p, _i), f in zip(self.mats, tc_flags) if f)
         # K extent of one tensor-core tile: long enough to amortise the pipeline ramp and the
         # epilogue, short enough that a small model still fills the GPU, and such that the last
         # wave of CTAs is nearly full (the block scheduler runs TC_CTAS_PER_SM per SM at a time)
@@ -149,26 +168,26 @@ class TilePlan:
         tc_k_nn = self._pick_tc_k(tc_mats, transposed=False)
         for mi, (gi, _pos, _idx) in enumerate(self.mats):
             g = self.plan.groups[gi]
-            v = 4 if vec_flags[mi] else 1
+            v = int(vec_widths[mi])
             if tc_flags[mi] and self.fin_tc_ok:
                 for r0 in range(0, g.n, 128):
                     for c0 in range(0, g.m, 64):
-                        fin["tc"].append((mi, r0, min(128, g.n - r0), c0, min(64, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
+                        fin["tc"].append((mi, r0, min(128, g.n - r0), c0, min(64, g.m - c0), 0, 1, 0, 0, v, (0, 0)))
             else:
                 for r0 in range(0, g.n, self.fin_rows):
                     for c0 in range(0, g.m, 128):
-                        fin[v].append((mi, r0, min(self.fin_rows, g.n - r0), c0, min(128, g.m - c0), 0, 1, 0, 0, (0, 0, 0)))
+                        fin["f"].append((mi, r0, min(self.fin_rows, g.n - r0), c0, min(128, g.m - c0), 0, 1, 0, 0, v, (0, 0)))
             if tc_flags[mi]:
                 row_blocks = _split_even(g.n, tc_k_nt, 32)
                 for c0 in range(0, g.m, 128):
                     for si, (r0, rows) in enumerate(row_blocks):
-                        nt["tc"].append((mi, r0, rows, c0, min(128, g.m - c0), si, len(row_blocks), ticket, tc_slots, (0, 0, 0)))
+                        nt["tc"].append((mi, r0, rows, c0, min(128, g.m - c0), si, len(row_blocks), ticket, tc_slots, v, (0, 0)))
                     ticket += 1
                     tc_slots += len(row_blocks)
                 col_blocks = _split_even(g.m, tc_k_nn, 32)
                 for r0 in range(0, g.n, 128):
                     for si, (c0, cols) in enumerate(col_blocks):
-                        nn["tc"].append((mi, r0, min(128, g.n - r0), c0, cols, si, len(col_blocks), ticket, tc_slots, (0, 0, 0)))
+                        nn["tc"].append((mi, r0, min(128, g.n - r0), c0, cols, si, len(col_blocks), ticket, tc_slots, v, (0, 0)))
                     ticket += 1
                     tc_slots += len(col_blocks)
                 continue
@@ -176,14 +195,14 @@ class TilePlan:
             for c0 in range(0, g.m, 128):
                 cols = min(128, g.m - c0)
                 for si, (r0, rows) in enumerate(row_blocks):
-                    nt[v].append((mi, r0, rows, c0, cols, si, len(row_blocks), ticket, nt_slots, (0, 0, 0)))
+                    nt["f"].append((mi, r0, rows, c0, cols, si, len(row_blocks), ticket, nt_slots, v, (0, 0)))
                 ticket += 1
                 nt_slots += len(row_blocks)
             col_blocks = _split_even(g.m, self.nn_cols_cap, 128)
             for r0 in range(0, g.n, self.nn_rows):
                 rows = min(self.nn_rows, g.n - r0)
                 for si, (c0, cols) in enumerate(col_blocks):
-                    nn[v].append((mi, r0, rows, c0, cols, si, len(col_blocks), ticket, nn_slots, (0, 0, 0)))
+                    nn["f"].append((mi, r0, rows, c0, cols, si, len(col_blocks), ticket, nn_slots, v, (0, 0)))
                 ticket += 1
                 nn_slots += len(col_blocks)
         self.n_tickets = max(ticket, 1)
@@ -296,13 +315,24 @@ class NativeCompressor:
         self.launches = 0  # kernels launched by the last aggregate()
         self._side_stream = torch.cuda.Stream(device=self.device)
         self._early = None  # (side, event) of an orthonormalisation issued by begin_step()
+        self._early_launches = 0
         # multi-GPU: factors are all-reduced by the product kernels themselves (peer pushes) plus
         # a small consumer kernel; PSGD_B200_COMM=nccl selects the library all-reduce instead
         self.comm = None
         if world_size() > 1 and os.environ.get("PSGD_B200_COMM", "p2p") == "p2p":
-            from .parallel.symm import Channel
+            from .parallel.symm import Channel, assert_same_on_all_ranks
 
+            # a rank with another model, rank or iteration count would push factors of another
+            # layout: find out now, with a message, instead of through a timeout later
+            assert_same_on_all_ranks(
+                (self.plan.signature(), int(core.config.rank), int(self.T)), "PowerSGD compression plan"
+            )
             self.comm = Channel(cap)
+        # status word of the tensor-core kernels' bounded waits: mapped pinned host memory, so the
+        # host can look at it every step without touching the GPU
+        from .parallel.symm import StatusWord
+
+        self._status = StatusWord()
 
     @staticmethod
     def _default_hyper() -> np.ndarray:
@@ -365,7 +395,13 @@ class NativeCompressor:
             d["hyper"] = 0 if hyper_index is None else hyper_index[idx]
             d["index"] = mi
             ptrs = [int(d["grad"]), int(d["param"]), int(d["mom"]), int(d["out"])]
-            vec.append(g.m % 4 == 0 and all(p % 16 == 0 for p in ptrs))
+            # widest global access every row of the matrix (and of its companions) allows
+            if g.m % 4 == 0 and all(p % 16 == 0 for p in ptrs):
+                vec.append(4)
+            elif g.m % 2 == 0 and all(p % 8 == 0 for p in ptrs):
+                vec.append(2)
+            else:
+                vec.append(1)
         assert where is not None
         self._mats_dev = _to_device(descs, self.device)
         # tensor-core (TMA + tcgen05) path: matrices TMA can address and that are worth it
@@ -375,7 +411,7 @@ class NativeCompressor:
         maps = np.zeros((len(self.tiles.mats), 256), dtype=np.uint8)
         for mi, (gi, _pos, idx) in enumerate(self.tiles.mats):
             g = self.plan.groups[gi]
-            ok = vec[mi] and g.n >= 128 and g.m >= 128 and mode != "ffma"
+            ok = vec[mi] == 4 and g.n >= 128 and g.m >= 128 and mode != "ffma"
             ok = ok and (mode == "tc" or hbm_bound or self.tiles.max_r >= 8)
             if ok:
                 buf = (ctypes.c_ubyte * 256)()
@@ -387,6 +423,7 @@ class NativeCompressor:
         self._tc_split = os.environ.get("PSGD_B200_TC_PRECISION", "split") != "tf32"
         self.uses_tensor_cores = any(tc)
         tile_arrays = self.tiles.build(vec, tc)
+        self._tile_arrays = tile_arrays
         self._tiles_dev: Dict[str, Dict[int, Tuple[torch.Tensor, int]]] = {}
         for name, by_vec in tile_arrays.items():
             self._tiles_dev[name] = {
@@ -394,13 +431,16 @@ class NativeCompressor:
             }
         self._partial = torch.empty(self.tiles.partial_floats, device=self.device, dtype=torch.float32)
         self._partial_tc = torch.empty(self.tiles.partial_tc_floats, device=self.device, dtype=torch.float32)
-        self._tc_status = torch.zeros(1, device=self.device, dtype=torch.int32)
         self._tickets = torch.zeros(self.tiles.n_tickets, device=self.device, dtype=torch.int32)
         self._out_views = out_views
         self._key = key
 
     # -- phases ----------------------------------------------------------------------------
-    def _orth(self, side: str, x: torch.Tensor, copy_to: torch.Tensor, prev: List[torch.Tensor], cm: List[torch.Tensor]):
+    def _orth(self, side: str, x: torch.Tensor, copy_to: torch.Tensor, prev: List[torch.Tensor], cm: List[torch.Tensor],
+              gather_to: Optional[torch.Tensor] = None):
+        """Orthonormalise `x` in place (mirrored into `copy_to`). With `gather_to`, `x` is first
+        filled with the sum over workers of the factor the previous product pushed (the sum is
+        also written to `gather_to`): the launch is the consumer of the in-kernel all-reduce."""
         code = self.lib.psgd_orth_launch(
             _ptr(self.units[side]),
             self.n_units[side],
@@ -416,12 +456,15 @@ class NativeCompressor:
             _ptr(self._orth_rinv),
             _ptr(self._orth_dead),
             _ptr(self._orth_tickets),
+            self.comm.ptr if gather_to is not None else ctypes.c_void_p(0),
+            _ptr(gather_to),
             _stream_ptr(),
         )
         native.check(code, "psgd_orth_launch")
         self.launches += 2  # Gram + factorisation, then the application of R^-1
 
-    def _gemm(self, transposed: bool, fin: torch.Tensor, fout: torch.Tensor, corr_fac, corr_c):
+    def _gemm(self, transposed: bool, fin: torch.Tensor, fout: torch.Tensor, corr_fac, corr_c,
+              fout2: Optional[torch.Tensor] = None):
         name = "nt" if transposed else "nn"
         tiles, count = self._tiles_dev[name]["tc"]
         if count:
@@ -435,30 +478,29 @@ class NativeCompressor:
                 _ptr(self._maps_dev),
                 _ptr(fin),
                 _ptr(fout),
+                _ptr(fout2),
                 len(corr_fac),
                 ctypes.cast(_ptr_array(corr_fac), ctypes.c_void_p),
                 ctypes.cast(_ptr_array(corr_c), ctypes.c_void_p),
                 _ptr(self._partial_tc),
                 _ptr(self._tickets),
                 self.comm.ptr if self.comm is not None else ctypes.c_void_p(0),
-                _ptr(self._tc_status),
+                self._status.dev_ptr,
                 _stream_ptr(),
             )
             native.check(code, "psgd_gemm_tc_launch")
             self.launches += 1
-        for v in (4, 1):
-            tiles, count = self._tiles_dev[name][v]
-            if count == 0:
-                continue
+        tiles, count = self._tiles_dev[name]["f"]
+        if count:
             code = self.lib.psgd_gemm_ffma_launch(
                 1 if transposed else 0,
-                1 if v == 4 else 0,
                 self.tiles.max_r,
                 _ptr(self._mats_dev),
                 _ptr(tiles),
                 count,
                 _ptr(fin),
                 _ptr(fout),
+                _ptr(fout2),
                 len(corr_fac),
                 ctypes.cast(_ptr_array(corr_fac), ctypes.c_void_p),
                 ctypes.cast(_ptr_array(corr_c), ctypes.c_void_p),
@@ -470,7 +512,18 @@ class NativeCompressor:
             native.check(code, "psgd_gemm_ffma_launch")
             self.launches += 1
 
-    def _finalize(self, sides: List[bool], fused_sgd: bool, workers: int):
+    def _gathers_in_finalize(self) -> bool:
+        """Multi-GPU: can the decompression launch gather the last factor from the channel itself?
+        Only the strip kernel does, and only when it is the sole decompression launch."""
+        if self.comm is None or world_size() == 1:
+            return False
+        if self._tiles_dev["fin"]["tc"][1]:
+            return False
+        return bool(self.lib.psgd_finalize_uses_strip(self.T, self.tiles.max_r, self.tiles.fin_rows, 0))
+
+    def _finalize(self, sides: List[bool], fused_sgd: bool, workers: int, gather_state: Optional[torch.Tensor] = None):
+        """`gather_state`: the warm-start buffer that receives the summed factor of the last
+        half-iteration when this launch is also its consumer (see `_gathers_in_finalize`)."""
         lloc, rloc, lsum, rsum = [], [], [], []
         for t, left in enumerate(sides):
             if left:
@@ -495,17 +548,15 @@ class NativeCompressor:
                 ctypes.cast(_ptr_array(rsum), ctypes.c_void_p),
                 1.0 / workers,
                 1 if fused_sgd else 0,
-                _ptr(self._tc_status),
+                self._status.dev_ptr,
                 _stream_ptr(),
             )
             native.check(code, "psgd_finalize_tc_launch")
             self.launches += 1
-        for v in (4, 1):
-            tiles, count = self._tiles_dev["fin"][v]
-            if count == 0:
-                continue
+        tiles, count = self._tiles_dev["fin"]["f"]
+        if count:
+            gather = gather_state is not None
             code = self.lib.psgd_finalize_launch(
-                1 if v == 4 else 0,
                 _ptr(self._mats_dev),
                 _ptr(tiles),
                 count,
@@ -519,15 +570,24 @@ class NativeCompressor:
                 ctypes.cast(_ptr_array(rsum), ctypes.c_void_p),
                 1.0 / workers,
                 1 if fused_sgd else 0,
+                self.comm.ptr if gather else ctypes.c_void_p(0),
+                0 if sides[-1] else 1,  # last half-iteration left: the fresh (summed) factor is the right one
+                _ptr(self.h_sum[len(sides) - 1]) if gather else ctypes.c_void_p(0),
+                _ptr(gather_state) if gather else ctypes.c_void_p(0),
                 _stream_ptr(),
             )
             native.check(code, "psgd_finalize_launch")
             self.launches += 1
 
-    def _half_iterations(self) -> List[bool]:
+    def _half_iterations(self):
+        """Runs the T half-iterations. Returns (sides, pending): `pending` is the warm-start buffer
+        whose summed factor the decompression launch still has to gather, or None."""
         core = self.core
         workers = world_size()
+        p2p = workers > 1 and self.comm is not None
+        defer_last = p2p and self._gathers_in_finalize()
         sides: List[bool] = []
+        pending: Optional[torch.Tensor] = None   # state buffer whose sum is still in the channel's slots
         for t in range(self.T):
             left = (core.step_counter * self.T + t) % 2 == 0
             sides.append(left)
@@ -542,6 +602,11 @@ class NativeCompressor:
                 same.append(in_side_i)
                 other.append(out_side_i)
             with _Range(f"psgd.iter{t}.orth"):
+                gather_to = None
+                if pending is not None:
+                    # the basis of this half-iteration IS the factor the previous product pushed
+                    assert pending is state_in
+                    gather_to, pending = self.h_sum[t - 1], None
                 if t == 0 and self._early is not None:
                     # the first basis was orthonormalised on the side stream while forward / backward ran
                     early_side, event = self._early
@@ -550,12 +615,15 @@ class NativeCompressor:
                     if early_side != side:  # state changed under us (e.g. a checkpoint was loaded): redo
                         self._orth(side, state_in, self.h_in[t], same, self.cmat[t])
                 else:
-                    self._orth(side, state_in, self.h_in[t], same, self.cmat[t])
+                    self._orth(side, state_in, self.h_in[t], same, self.cmat[t], gather_to)
             with _Range(f"psgd.iter{t}.product"):
-                self._gemm(left, self.h_in[t], self.h_loc[t], other, self.cmat[t])
+                # one worker: the product is final, so the kernel also writes the warm-start buffer
+                self._gemm(left, self.h_in[t], self.h_loc[t], other, self.cmat[t], state_out if workers == 1 else None)
             total = state_out.numel()
             with _Range(f"psgd.iter{t}.reduce"):
-                if workers > 1 and self.comm is not None:
+                if p2p and (t < self.T - 1 or defer_last):
+                    pending = state_out  # gathered by the next consumer of that factor
+                elif p2p:
                     code = self.lib.psgd_factor_reduce_launch(
                         self.comm.ptr, ctypes.c_longlong(total), _ptr(self.h_sum[t]), _ptr(state_out), _stream_ptr()
                     )
@@ -565,9 +633,7 @@ class NativeCompressor:
                     self.h_sum[t][:total].copy_(self.h_loc[t][:total])
                     self._allreduce_sum(self.h_sum[t][:total])
                     state_out.copy_(self.h_sum[t][:total])
-                else:
-                    state_out.copy_(self.h_loc[t][:total])
-        return sides
+        return sides, pending
 
     def _allreduce_sum(self, flat: torch.Tensor) -> None:
         dist.all_reduce(flat)
@@ -590,7 +656,9 @@ class NativeCompressor:
         fork.record(main)
         self._side_stream.wait_event(fork)
         with torch.cuda.stream(self._side_stream):
+            before = self.launches
             self._orth(side, state_in, self.h_in[0], [], self.cmat[0])
+            self._early_launches = self.launches - before  # counted with the step that uses them
             done = torch.cuda.Event()
             done.record(self._side_stream)
         self._early = (side, done)
@@ -601,18 +669,27 @@ class NativeCompressor:
             self.comm.close()
             self.comm = None
 
+    def check(self) -> None:
+        """Raise `PowerSGDCommTimeout` if a bounded device-side wait of an EARLIER launch gave up
+        (a peer that never pushed, a tensor-core pipeline that stalled). Plain host reads of
+        mapped pinned words: no synchronisation, cheap enough for every step."""
+        if self.comm is not None:
+            self.comm.check()
+        self._status.check("a tensor-core pipeline wait")
+
     # -- public ----------------------------------------------------------------------------
     def aggregate(self, gradients: List[torch.Tensor]) -> List[torch.Tensor]:
-        self.launches = 0
+        self.check()
+        self.launches = self._early_launches if self._early is not None else 0
         self._bind(gradients)
         workers = world_size()
         if workers == 1:
             saved = self.h_sum
             self.h_sum = self.h_loc
         try:
-            sides = self._half_iterations()
+            sides, pending = self._half_iterations()
             with _Range("psgd.finalize"):
-                self._finalize(sides, fused_sgd=False, workers=workers)
+                self._finalize(sides, fused_sgd=False, workers=workers, gather_state=pending)
         finally:
             if workers == 1:
                 self.h_sum = saved
@@ -628,7 +705,8 @@ class NativeCompressor:
     ) -> None:
         """Same as `aggregate`, but applies SGD to `params` inside the last kernel instead of
         materialising the averaged gradients."""
-        self.launches = 0
+        self.check()
+        self.launches = self._early_launches if self._early is not None else 0
         self._bind(gradients, params, moms, hyper_index, need_out=False)
         workers = world_size()
         keep = self._hyper_dev
@@ -637,9 +715,9 @@ class NativeCompressor:
             saved = self.h_sum
             self.h_sum = self.h_loc
         try:
-            sides = self._half_iterations()
+            sides, pending = self._half_iterations()
             with _Range("psgd.finalize+sgd"):
-                self._finalize(sides, fused_sgd=True, workers=workers)
+                self._finalize(sides, fused_sgd=True, workers=workers, gather_state=pending)
         finally:
             self._hyper_dev = keep
             if workers == 1:
@@ -666,6 +744,12 @@ class NativeFlatAllReduce:
         self.path = "local"
         self.n_pad = 0
         self._bulk_layout = None
+        self._pushed = False  # one-shot path: this step's pack + push already left with another launch
+
+    def check(self) -> None:
+        """Raise `PowerSGDCommTimeout` if a bounded wait of an earlier launch gave up."""
+        if self.comm is not None:
+            self.comm.check()
 
     def _bind(self, grads, params=None, moms=None, hyper_index=None, need_out=True):
         key = (
@@ -709,6 +793,7 @@ class NativeFlatAllReduce:
         pointers = [int(items[name][i]) for name in ("grad", "param", "mom", "out") for i in range(len(grads))]
         self._vec = 1 if all(ptr % 16 == 0 for ptr in pointers) else 0
         self._items_dev = _to_device(items, device)
+        self._items_host = items
         self._block_item = _to_device(np.asarray(block_item, dtype=np.int32), device)
         self._block_first = _to_device(np.asarray(block_first, dtype=np.int32), device)
         self._nblocks = len(block_item)
@@ -782,7 +867,10 @@ class NativeFlatAllReduce:
             self.launches += 2
             self._launch(13 if sgd else 12, hyper_dev, 1.0)
         elif self.path == "oneshot":
-            self._launch(5, hyper_dev, float(workers))
+            if self._pushed:
+                self._pushed = False
+            else:
+                self._launch(5, hyper_dev, float(workers))
             self._launch(7 if sgd else 6, hyper_dev, 1.0)
         else:
             self._launch(0, hyper_dev, float(workers))
@@ -790,12 +878,14 @@ class NativeFlatAllReduce:
             self._launch(2 if sgd else 1, hyper_dev, 1.0)
 
     def aggregate(self, gradients: List[torch.Tensor]) -> List[torch.Tensor]:
+        self.check()
         self.launches = 0
         self._bind(gradients)
         self._run(self._hyper_dev, world_size(), sgd=False)
         return list(self._views)
 
     def aggregate_and_step(self, gradients, params, moms, hyper_index, hyper_dev) -> None:
+        self.check()
         self.launches = 0
         self._bind(gradients, params, moms, hyper_index, need_out=False)
         self._run(hyper_dev, world_size(), sgd=True)
@@ -815,18 +905,23 @@ class MultiTensorAccumulate:
     Error feedback keeps the compression residual in `p.grad` and lets autograd accumulate the
     next gradient onto it (powersgd/__init__.py:17-25), which costs one small add kernel per
     parameter. A training step that owns the loop detaches the residuals before backward, lets
-    autograd adopt the fresh gradients without arithmetic, and folds them in with this kernel."""
+    autograd adopt the fresh gradients without arithmetic, and folds them in with this kernel.
+
+    Multi-GPU: the same launch can carry the first half of the flat all-reduce of the uncompressed
+    tensors (`push=`): their gradients are scaled, zeroed and pushed into every peer's slots while
+    the residuals are folded, so that the data is on its way before the low-rank kernels start."""
 
     def __init__(self):
         self.lib = native.lib()
         self._key = None
 
-    def __call__(self, dst: Sequence[torch.Tensor], src: Sequence[torch.Tensor]) -> None:
-        key = (tuple(t.data_ptr() for t in dst), tuple(t.data_ptr() for t in src))
+    def __call__(self, dst: Sequence[torch.Tensor], src: Sequence[torch.Tensor], push: "Optional[NativeFlatAllReduce]" = None) -> None:
+        key = (tuple(t.data_ptr() for t in dst), tuple(t.data_ptr() for t in src), None if push is None else push._key)
         if key != self._key:
             device = dst[0].device
             per_block = self.lib.psgd_flat_block_elems()
-            items = np.zeros(len(dst), dtype=layout.FLAT_DTYPE)
+            pushed = [] if push is None else list(np.frombuffer(push._items_host.tobytes(), dtype=layout.FLAT_DTYPE))
+            items = np.zeros(len(dst) + len(pushed), dtype=layout.FLAT_DTYPE)
             block_item, block_first = [], []
             for i, (d, s_) in enumerate(zip(dst, src)):
                 if not same_layout(d, s_) or d.dtype != torch.float32 or s_.dtype != torch.float32:
@@ -834,7 +929,12 @@ class MultiTensorAccumulate:
                 if not is_dense(d):
                     raise ValueError("accumulate needs dense tensors")
                 items[i]["grad"], items[i]["out"], items[i]["numel"] = s_.data_ptr(), d.data_ptr(), d.numel()
-                for first in range(0, d.numel(), per_block):
+                items[i]["op"] = 8
+            for j, it in enumerate(pushed):
+                items[len(dst) + j] = it
+                items[len(dst) + j]["op"] = 5
+            for i in range(len(items)):
+                for first in range(0, int(items[i]["numel"]), per_block):
                     block_item.append(i)
                     block_first.append(first)
             self._vec = 1 if all(ptr % 16 == 0 for ptr in key[0] + key[1]) else 0
@@ -845,10 +945,13 @@ class MultiTensorAccumulate:
             self._hyper = _to_device(NativeCompressor._default_hyper(), device)
             self._key = key
         code = self.lib.psgd_flat_launch(
-            8, self._vec, _ptr(self._items), _ptr(self._block_item), _ptr(self._block_first), self._nblocks,
-            _ptr(self._hyper), ctypes.c_void_p(0), 1.0, ctypes.c_void_p(0), ctypes.c_longlong(0), _stream_ptr(),
+            8 if push is None else 9, self._vec, _ptr(self._items), _ptr(self._block_item), _ptr(self._block_first),
+            self._nblocks, _ptr(self._hyper), ctypes.c_void_p(0), 1.0 if push is None else float(world_size()),
+            ctypes.c_void_p(0) if push is None else push.comm.ptr, ctypes.c_longlong(0), _stream_ptr(),
         )
         native.check(code, "psgd_flat_launch")
+        if push is not None:
+            push._pushed = True
 
 
 class FusedSGDDriver:
@@ -940,7 +1043,34 @@ class FusedSGDDriver:
         ev.record()
         self._slot_events[i] = ev
 
+    def check(self) -> None:
+        """Raise `PowerSGDCommTimeout` if any bounded device-side wait of an earlier step gave up:
+        a peer that stayed away leaves zeros in place of its contribution, so the step that
+        follows must not run. Host reads of mapped pinned words only; called every step."""
+        core = self.agg._powersgd
+        if core._native is not None:
+            core._native.check()
+        self._flat_all.check()
+        self._flat_plain.check()
+
+    def fold(self, accumulate: "MultiTensorAccumulate", dst: Sequence[torch.Tensor], src: Sequence[torch.Tensor]) -> None:
+        """`dst[i] += src[i]` (residual + fresh gradient) in one launch which, on several GPUs in
+        the compression phase, also packs and pushes the uncompressed tensors' gradients."""
+        agg = self.agg
+        push = None
+        if world_size() > 1 and agg.step_counter >= agg.config.start_compressing_after_num_steps and getattr(self, "_params", None):
+            mask = agg.is_compressed_mask
+            pick = lambda xs: [x for x, k in zip(xs, mask) if not k]  # noqa: E731
+            plain = [p.grad for p in pick(self._params)]
+            if plain and all(g is not None for g in plain):
+                flat = self._flat_plain
+                flat._bind([g.data for g in plain], pick(self._params), pick(self._moms), pick(self._index), need_out=False)
+                if flat.path == "oneshot":
+                    push = flat
+        accumulate(dst, src, push=push)
+
     def step(self, optimizer, prepared: bool = False) -> None:
+        self.check()
         if not prepared:
             self.prepare(optimizer)
         # the gradient tensors may have been replaced since the last step (dropped zero gradients

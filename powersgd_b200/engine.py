@@ -40,6 +40,7 @@ class TrainStep:
         channels_last: bool = True,
         grad_clip: Optional[float] = None,
         autotune: bool = True,
+        time_aggregate: bool = True,
     ):
         self.model = model
         self.loss_fn = loss_fn
@@ -48,8 +49,8 @@ class TrainStep:
         self.device = next(model.parameters()).device
         self.use_graph = bool(cuda_graph) and self.device.type == "cuda"
         self.eager_steps = max(int(eager_steps), 2)
-        # 4-D inputs are fed in NHWC: cuDNN's tensor-core convolutions run ~1.7x faster on
-        # B200 that way, while parameters and their gradients stay contiguous [out, in*kh*kw].
+        # 4-D inputs are fed in NHWC (cuDNN's tensor-core convolutions run ~1.7x faster on B200 that
+        # way) and 4-D weights, their gradients and momentum buffers are stored channels_last too.
         self.channels_last = bool(channels_last) and self.device.type == "cuda"
         if self.channels_last:
             self._weights_to_channels_last()
@@ -62,11 +63,17 @@ class TrainStep:
             torch.backends.cudnn.benchmark = True
         self._steps_done = 0
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self._graph_keep: Dict[int, list] = {}
         self._static_x: Optional[torch.Tensor] = None
         self._static_y: Optional[torch.Tensor] = None
         self._static_loss: Optional[torch.Tensor] = None
         self._pool = None
         self._agg_events = None
+        # Device time between the end of backward and the end of the parameter update. Eager steps
+        # bracket it with ordinary events; a recorded step carries two event-record nodes
+        # ("external" events, which a graph replays), so every replay refreshes the pair.
+        self.time_aggregate = bool(time_aggregate) and self.device.type == "cuda"
+        self._graph_events: Dict[int, tuple] = {}
         self.launches_per_step = 0
         # residuals detached from p.grad for the duration of backward: (parameter, residual)
         self._held: list = []
@@ -137,7 +144,11 @@ class TrainStep:
                 from .cuda_path import MultiTensorAccumulate
 
                 self._accumulate = MultiTensorAccumulate()
-            self._accumulate([r for _p, r in live], [p.grad for p, _r in live])
+            fused = getattr(self.aggregator, "_fused", None)
+            if fused is not None:
+                fused.fold(self._accumulate, [r for _p, r in live], [p.grad for p, _r in live])
+            else:
+                self._accumulate([r for _p, r in live], [p.grad for p, _r in live])
             self._fold_launches = 1
         else:
             for p, r in live:
@@ -149,16 +160,19 @@ class TrainStep:
         self._begin()
         loss = self.loss_fn(self.model(self._format(x)), y)
         loss.backward()
-        self._fold()
-        self._clip()
-        if time_aggregate and self.device.type == "cuda":
+        if time_aggregate and self.time_aggregate:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
+            self._fold()
+            self._clip()
             optimizer_step(self.optimizer, self.aggregator)
             b.record()
             self._agg_events = (a, b)
         else:
+            self._fold()
+            self._clip()
             optimizer_step(self.optimizer, self.aggregator)
+            self._agg_events = None
         fused = getattr(self.aggregator, "_fused", None)
         if fused is not None:
             self.launches_per_step = getattr(fused, "launches", 0) + getattr(self, "_fold_launches", 0)
@@ -166,7 +180,8 @@ class TrainStep:
 
     @property
     def aggregate_ms(self) -> Optional[float]:
-        """Device time of the aggregation + optimizer part of the last eagerly run step."""
+        """Device time of the aggregation + optimizer part (everything after backward) of the LAST
+        step, recorded or eager; synchronises on that step's end. None if it was not timed."""
         if self._agg_events is None:
             return None
         a, b = self._agg_events
@@ -194,20 +209,29 @@ class TrainStep:
         core = getattr(agg, "_powersgd", None)
         if core is not None and core.params:
             core.step_counter += 1
+        self.optimizer._opt_called = True  # what a learning-rate scheduler checks
 
     def _capture(self, parity: int) -> None:
         agg = self.aggregator
         saved = (agg.step_counter, agg._powersgd.step_counter)
+        from .cuda_path import capture_scope
+
         graph = torch.cuda.CUDAGraph()
         torch.cuda.synchronize()
         # relaxed: descriptor tables rebuilt during capture allocate pinned staging memory
-        with torch.cuda.graph(graph, pool=self._pool, capture_error_mode="relaxed"):
+        with capture_scope() as keep, torch.cuda.graph(graph, pool=self._pool, capture_error_mode="relaxed"):
             self._begin()
             loss = self.loss_fn(self.model(self._static_x), self._static_y)
             loss.backward()
+            if self.time_aggregate:
+                ev = (torch.cuda.Event(enable_timing=True, external=True), torch.cuda.Event(enable_timing=True, external=True))
+                ev[0].record()
             self._fold()
             self._clip()
             agg.fused_step(self.optimizer, prepared=True)
+            if self.time_aggregate:
+                ev[1].record()
+                self._graph_events[parity] = ev
             if self._static_loss is None:
                 self._static_loss = loss.detach()
             else:
@@ -217,6 +241,7 @@ class TrainStep:
         # capturing ran the host side of the step (counters) but not the kernels: rewind
         agg.step_counter, agg._powersgd.step_counter = saved
         self._graphs[parity] = graph
+        self._graph_keep[parity] = keep  # tables the graph's copy nodes read: same lifetime as the graph
 
     def __call__(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
         if not self._graphable_now():
@@ -235,9 +260,17 @@ class TrainStep:
         parity = self._parity()
         if parity not in self._graphs:
             self._capture(parity)
+        # a bounded device-side wait that gave up during an earlier step (a peer that stayed away)
+        # left zeros where data should be: stop here, with the step number, instead of training on
+        fused = self.aggregator._fused
+        try:
+            fused.check()
+        except RuntimeError as exc:
+            raise type(exc)(f"training step {self._steps_done}: {exc}") from None
         # host-side refresh of what the graph reads from memory (learning rates etc.)
-        self.aggregator._fused.prepare(self.optimizer)
+        fused.prepare(self.optimizer)
         self._graphs[parity].replay()
+        self._agg_events = self._graph_events.get(parity)
         self._bump_counters()
         self._steps_done += 1
         return self._static_loss

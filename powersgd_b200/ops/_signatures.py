@@ -14,7 +14,7 @@ def declare(lib) -> None:
     lib.psgd_device_info.argtypes = [C.POINTER(i32)] * 4
 
     lib.psgd_orth_launch.restype = i32
-    lib.psgd_orth_launch.argtypes = [vp, i32, vp, i32, i32, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp]
+    lib.psgd_orth_launch.argtypes = [vp, i32, vp, i32, i32, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]
 
     lib.psgd_gemm_nn_tile_rows.restype = i32
     lib.psgd_gemm_nn_tile_rows.argtypes = [i32]
@@ -23,10 +23,12 @@ def declare(lib) -> None:
     lib.psgd_gemm_template_rank.restype = i32
     lib.psgd_gemm_template_rank.argtypes = [i32]
     lib.psgd_gemm_ffma_launch.restype = i32
-    lib.psgd_gemm_ffma_launch.argtypes = [i32, i32, i32, vp, vp, i32, vp, vp, i32, vp, vp, vp, vp, vp, vp]
+    lib.psgd_gemm_ffma_launch.argtypes = [i32, i32, vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp]
 
     lib.psgd_finalize_launch.restype = i32
-    lib.psgd_finalize_launch.argtypes = [i32, vp, vp, i32, i32, i32, vp, i32, vp, vp, vp, vp, f32, i32, vp]
+    lib.psgd_finalize_launch.argtypes = [vp, vp, i32, i32, i32, vp, i32, vp, vp, vp, vp, f32, i32, vp, i32, vp, vp, vp]
+    lib.psgd_finalize_uses_strip.restype = i32
+    lib.psgd_finalize_uses_strip.argtypes = [i32, i32, i32, i32]
 
     lib.psgd_flat_block_elems.restype = i32
     lib.psgd_flat_block_elems.argtypes = []
@@ -47,7 +49,7 @@ _OPTIONAL = {
     "psgd_sign_vote": (i32, [vp, i32, i64, i32, vp, vp, vp]),
     "psgd_gemm_tc_rank_pad": (i32, [i32]),
     "psgd_tma_encode_matrix": (i32, [vp, vp, i32, i32]),
-    "psgd_gemm_tc_launch": (i32, [i32, i32, i32, vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp]),
+    "psgd_gemm_tc_launch": (i32, [i32, i32, i32, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp]),
     "psgd_finalize_strip_rows": (i32, [i32, i32]),
     "psgd_orth_template_rank": (i32, [i32]),
     "psgd_orth_chunk_rows": (i32, [i32]),

@@ -40,7 +40,8 @@ TILE_DTYPE = np.dtype(
         ("nsplit", "<i4"),
         ("ticket", "<i4"),
         ("slot0", "<i4"),
-        ("pad", "<i4", (3,)),
+        ("vec", "<i4"),
+        ("pad", "<i4", (2,)),
     ]
 )
 assert TILE_DTYPE.itemsize == 48
@@ -68,7 +69,8 @@ FLAT_DTYPE = np.dtype(
         ("numel", "<i8"),
         ("flat_off", "<i8"),
         ("hyper", "<i4"),
-        ("pad", "<i4", (3,)),
+        ("op", "<i4"),
+        ("pad", "<i4", (2,)),
     ]
 )
 assert FLAT_DTYPE.itemsize == 64

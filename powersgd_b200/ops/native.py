@@ -52,6 +52,20 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+def use_for_cuda() -> bool:
+    """Gate for ops that have a PyTorch restatement: True when the native kernels should run for a
+    CUDA tensor. A missing library on a CUDA machine is an error, not a silent slow path, unless
+    PSGD_B200_ALLOW_FALLBACK=1 opts into the PyTorch restatement."""
+    if available():
+        return True
+    if os.environ.get("PSGD_B200_ALLOW_FALLBACK", "0") == "1":
+        return False
+    raise RuntimeError(
+        f"powersgd_b200: a CUDA tensor was given but the native sm_100a library is not loadable ({load_error()}); "
+        "build it with `python -m powersgd_b200.csrc.build` or set PSGD_B200_ALLOW_FALLBACK=1"
+    )
+
+
 def check(code: int, what: str) -> None:
     if code != 0:
         msg = lib().psgd_last_error()

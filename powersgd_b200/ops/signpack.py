@@ -19,7 +19,7 @@ def _words(numel: int) -> int:
 
 
 def _use_native(t: torch.Tensor) -> bool:
-    return t.is_cuda and native.available()
+    return t.is_cuda and native.use_for_cuda()
 
 
 def _stream():

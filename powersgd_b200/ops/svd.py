@@ -29,7 +29,7 @@ def _torch_svd(m: torch.Tensor):
 def svd_many(matrices: Sequence[torch.Tensor]) -> List[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]:
     results: List = [None] * len(matrices)
     batch = []  # (index, tall matrix [n, c], transposed?)
-    use_native = bool(matrices) and matrices[0].is_cuda and native.available()
+    use_native = bool(matrices) and matrices[0].is_cuda and native.use_for_cuda()
     max_c = native.lib().psgd_svd_tall_max_cols() if use_native else 0
     for i, m in enumerate(matrices):
         n, c = m.shape

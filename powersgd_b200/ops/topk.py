@@ -2,8 +2,9 @@
 
 `topk_abs(x, k, memory=None)` returns `(values, positions)` of the k entries of the flattened
 tensor with the largest |x| (order unspecified, positions int32) and, when `memory` is given,
-fills it with x where the taken entries are zeroed. On CPU, or without the native library, the
-same result comes from `torch.topk` (gradient_reducers.py:240-253 is the reference sequence).
+fills it with x where the taken entries are zeroed. On CPU (or on CUDA without the native
+library when PSGD_B200_ALLOW_FALLBACK=1 allows it; otherwise that is an error) the same result
+comes from `torch.topk` (gradient_reducers.py:240-253 is the reference sequence).
 """
 from __future__ import annotations
 
@@ -21,7 +22,7 @@ def topk_abs(x: torch.Tensor, k: int, memory: Optional[torch.Tensor] = None) -> 
     flat = x.reshape(-1)
     n = flat.numel()
     k = int(k)
-    if flat.is_cuda and native.available() and flat.dtype == torch.float32 and flat.is_contiguous() and (
+    if flat.is_cuda and native.use_for_cuda() and flat.dtype == torch.float32 and flat.is_contiguous() and (
         memory is None or (memory.is_contiguous() and memory.dtype == torch.float32)
     ):
         lib = native.lib()

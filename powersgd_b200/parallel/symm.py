@@ -29,8 +29,70 @@ class PowerSGDCommTimeout(RuntimeError):
     """A bounded device-side wait on a peer ran out."""
 
 
+class PowerSGDConfigMismatch(RuntimeError):
+    """The ranks of a job were set up differently (model shapes, rank, iterations per step)."""
+
+
 def _vp(x: int) -> ctypes.c_void_p:
     return ctypes.c_void_p(int(x))
+
+
+def assert_same_on_all_ranks(obj, what: str, group=None) -> None:
+    """Collective: every rank contributes `obj` (anything picklable and comparable); raises
+    `PowerSGDConfigMismatch` on EVERY rank when they differ. Called once when multi-rank state is
+    set up, so that a rank with another model or configuration is reported by name instead of
+    showing up later as a peer whose data never arrives. Works on any backend (host objects)."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return
+    world = dist.get_world_size(group)
+    gathered: List[Optional[object]] = [None] * world
+    dist.all_gather_object(gathered, obj, group=group)
+    odd = [r for r, other in enumerate(gathered) if other != gathered[0]]
+    if odd:
+        raise PowerSGDConfigMismatch(
+            f"{what} differs between ranks: ranks {odd} disagree with rank 0 "
+            f"(this is rank {dist.get_rank(group)})"
+        )
+
+
+class StatusWord:
+    """One int in mapped pinned host memory that kernels write (through `dev_ptr`) when a bounded
+    wait gives up; the host reads it without touching the GPU."""
+
+    def __init__(self):
+        self.lib = native.lib()
+        host_ptr, dev_ptr = ctypes.POINTER(ctypes.c_int)(), ctypes.POINTER(ctypes.c_int)()
+        native.check(self.lib.psgd_status_alloc(ctypes.byref(host_ptr), ctypes.byref(dev_ptr)), "psgd_status_alloc")
+        self._host = host_ptr
+        self._dev = ctypes.cast(dev_ptr, ctypes.c_void_p).value
+
+    @property
+    def dev_ptr(self) -> ctypes.c_void_p:
+        return _vp(self._dev)
+
+    @property
+    def value(self) -> int:
+        return int(self._host[0]) if self._host else 0
+
+    def set(self, code: int) -> None:
+        """Host-side write (tests inject a failure this way; `set(0)` clears)."""
+        self._host[0] = int(code)
+
+    def check(self, what: str) -> None:
+        code = self.value
+        if code != 0:
+            raise PowerSGDCommTimeout(f"{what} gave up on the device (status {code})")
+
+    def close(self) -> None:
+        if self._host:
+            self.lib.psgd_status_free(self._host)
+            self._host = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def default_timeout_ms() -> float:
@@ -116,10 +178,8 @@ class Channel:
         self.slots = SymmetricBuffer(2 * self.world * self.cap * 8, group)
         # local bookkeeping words: epoch, arrival counters
         self._words = torch.zeros(16, dtype=torch.int32, device=device)
-        host_ptr, dev_ptr = ctypes.POINTER(ctypes.c_int)(), ctypes.POINTER(ctypes.c_int)()
-        native.check(self.lib.psgd_status_alloc(ctypes.byref(host_ptr), ctypes.byref(dev_ptr)), "psgd_status_alloc")
-        self._status_host = host_ptr
-        self._status_dev = ctypes.cast(dev_ptr, ctypes.c_void_p).value
+        self._status = StatusWord()
+        self._status_dev = self._status._dev
         nbytes = self.lib.psgd_comm_desc_bytes()
         host_desc = (ctypes.c_ubyte * nbytes)()
         slots = (ctypes.c_void_p * self.world)(*self.slots.ptrs)
@@ -140,7 +200,7 @@ class Channel:
 
     @property
     def status(self) -> int:
-        return int(self._status_host[0])
+        return self._status.value
 
     def check(self) -> None:
         code = self.status
@@ -150,7 +210,7 @@ class Channel:
             )
 
     def reset_status(self) -> None:
-        self._status_host[0] = 0
+        self._status.set(0)
         self._words[8] = 0
 
     def all_reduce_(self, tensor: torch.Tensor, scale: float = 1.0, max_blocks: int = 296) -> torch.Tensor:
@@ -169,9 +229,7 @@ class Channel:
 
     def close(self) -> None:
         self.slots.close()
-        if self._status_host:
-            self.lib.psgd_status_free(self._status_host)
-            self._status_host = None
+        self._status.close()
 
 
 class BulkAllReduce:

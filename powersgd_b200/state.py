@@ -22,6 +22,7 @@ Factors and residuals are stored per shape group, which is also how the kernels 
 """
 from __future__ import annotations
 
+import warnings
 from typing import Dict, Optional, Sequence
 
 import torch
@@ -41,6 +42,7 @@ def compressor_state_dict(core, gradients: Optional[Sequence[torch.Tensor]] = No
             "error": None,
         }
         if gradients is not None:
+            # logical order ([shape[0], rest] of the contiguous view), whatever the memory format
             entry["error"] = torch.stack(
                 [gradients[i].detach().reshape(g.n, g.m) for i in g.members]
             ).cpu()
@@ -68,13 +70,20 @@ def load_compressor_state_dict(core, state: Dict, gradients: Optional[Sequence[t
         core._qs[gi].copy_(entry["q"].to(core.device))
         if gradients is not None and entry.get("error") is not None:
             for pos, idx in enumerate(g.members):
-                gradients[idx].reshape(g.n, g.m).copy_(entry["error"][pos].to(gradients[idx].device))
+                # write through the tensor itself: `reshape` of a channels_last gradient would
+                # return a copy and the restored residual would be lost
+                dst = gradients[idx]
+                dst.copy_(entry["error"][pos].to(dst.device).view(dst.shape))
     core.step_counter = int(state["step_counter"])
+    native = getattr(core, "_native", None)
+    if native is not None:
+        native._early = None  # a basis orthonormalised ahead of time came from the factors just replaced
     try:
         core.generator.set_state(state["generator_state"].cpu())
-    except RuntimeError:
-        # a generator state only restores onto the device type that produced it
-        pass
+    except RuntimeError as exc:
+        # a generator state only restores onto the device type that produced it; the generator is
+        # only used to draw the initial factors, which the checkpoint has just overwritten
+        warnings.warn(f"PowerSGD checkpoint: generator state not restored ({exc})")
 
 
 def aggregator_state_dict(agg, gradients: Optional[Sequence[torch.Tensor]] = None) -> Dict:

@@ -266,6 +266,74 @@ def scenario_train_step_graph():
         print("SCENARIO-OK", losses[0], losses[-1])
 
 
+def scenario_train_step_timeout():
+    """A rank stays away from a training step: the others' bounded device-side waits give up, and
+    their NEXT call of the training step raises (naming the step) instead of applying an update
+    that is missing a contribution. Made on the host: nothing faults, traps or hangs a GPU, and
+    the rank that stays away leaves nothing in flight."""
+    import datetime
+
+    rank, world, dev = _init("nccl")
+    from powersgd_b200 import Config, PowerSGD
+    from powersgd_b200.engine import TrainStep
+    from powersgd_b200.parallel.symm import PowerSGDCommTimeout
+
+    assert float(os.environ.get("PSGD_B200_COMM_TIMEOUT_MS", "0")) <= 1000, "run this scenario with a short limit"
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(128, 256), torch.nn.ReLU(), torch.nn.Linear(256, 10)).to(dev)
+    params = list(model.parameters())
+    opt = torch.optim.SGD(params, lr=0.05, momentum=0.9)
+    agg = PowerSGD(params, Config(rank=2, num_iters_per_step=2, start_compressing_after_num_steps=0))
+    step = TrainStep(model, torch.nn.functional.cross_entropy, opt, agg, cuda_graph=True)
+    x, y = torch.randn(32, 128, device=dev), torch.randint(0, 10, (32,), device=dev)
+    for _ in range(5):
+        step(x, y).item()
+    assert step._graphs
+    torch.cuda.synchronize()
+    dist.barrier()
+    store = dist.distributed_c10d._get_default_store()
+    if rank == world - 1:
+        # stays away, between steps, with nothing of its own in flight
+        store.wait(["timeout-observed"], datetime.timedelta(seconds=120))
+    else:
+        raised_after = None
+        for extra in range(3):
+            try:
+                step(x, y).item()
+            except PowerSGDCommTimeout as exc:
+                raised_after = extra
+                assert "training step" in str(exc)
+                break
+        assert raised_after is not None and raised_after <= 2, raised_after
+        # the device still answers
+        assert torch.arange(10, device=dev).sum().item() == 45
+        if rank == 0:
+            store.set("timeout-observed", "1")
+    dist.barrier()
+    agg.close()
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
+def scenario_plan_mismatch_gloo():
+    """Ranks that were set up differently are told so at construction, on every rank."""
+    rank, world, dev = _init("gloo")
+    from powersgd_b200.parallel.symm import PowerSGDConfigMismatch, assert_same_on_all_ranks
+    from powersgd_b200.plan import CompressionPlan
+
+    assert_same_on_all_ranks((CompressionPlan.build([(64, 27), (10, 512)], rank=2).signature(), 2, 2), "plan")
+    shapes = [(64, 27), (10, 512)] if rank == 0 else [(64, 27), (12, 512)]
+    raised = False
+    try:
+        assert_same_on_all_ranks((CompressionPlan.build(shapes, rank=2).signature(), 2, 2), "PowerSGD compression plan")
+    except PowerSGDConfigMismatch as exc:
+        raised = "compression plan" in str(exc)
+    assert raised
+    dist.barrier()
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
 def scenario_mlp_gloo():
     """The plumbing configuration: 2-layer MLP on CPU ranks; parameters stay bit-identical."""
     rank, world, dev = _init("gloo")

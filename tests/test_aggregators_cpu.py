@@ -155,6 +155,26 @@ def test_state_dict_roundtrip_continues_identically():
         bad.load_state_dict(state)
 
 
+def test_state_dict_restores_residuals_into_channels_last_gradients():
+    """Convolution gradients stored channels_last (what TrainStep does on CUDA) are not viewable as
+    [n, m] in logical order: the restore has to write through the tensor itself."""
+    torch.manual_seed(2)
+    params = [torch.zeros(16, 8, 3, 3), torch.zeros(10, 40)]
+    cfg = Config(rank=2, min_compression_rate=2, start_compressing_after_num_steps=0)
+    a = PowerSGD(params, cfg)
+    fmt = torch.channels_last
+    grads = [torch.randn(16, 8, 3, 3).contiguous(memory_format=fmt), torch.randn(10, 40)]
+    a.aggregate(grads)  # leaves non-zero residuals
+    assert float(grads[0].abs().sum()) > 0
+    state = copy.deepcopy(a.state_dict(grads))
+    b = PowerSGD(params, cfg)
+    restored = [torch.zeros(16, 8, 3, 3).contiguous(memory_format=fmt), torch.zeros(10, 40)]
+    b.load_state_dict(state, restored)
+    for x, y in zip(grads, restored):
+        assert torch.equal(x, y)
+    assert restored[0].is_contiguous(memory_format=fmt)
+
+
 @pytest.mark.parametrize("rank,iters,steps", [(1, 1, 3), (2, 2, 3), (4, 3, 4), (2, 1, 5)])
 def test_matches_reference_library_bitwise(rank, iters, steps):
     ref = reference_library()

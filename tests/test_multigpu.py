@@ -30,3 +30,11 @@ def test_two_gpu_library_allreduce_path():
     """PSGD_B200_COMM=nccl: same kernels, factors and flat buffer reduced by the library (eager)."""
     res = run_scenario("powersgd_native_nccl", nproc=2, timeout=600, env=dict(ENV, PSGD_B200_COMM="nccl"))
     assert "SCENARIO-OK" in res.stdout, res.stdout[-3000:] + res.stderr[-6000:]
+
+
+@needs_two
+def test_two_gpu_training_step_raises_when_a_peer_stays_away():
+    """Failure detection in the product: 300 ms limit on device-side waits, library NVLS off, the
+    in-kernel collectives on plain peer stores."""
+    res = run_scenario("train_step_timeout", nproc=2, timeout=600, env=dict(ENV, PSGD_B200_COMM_TIMEOUT_MS="300"))
+    assert "SCENARIO-OK" in res.stdout, res.stdout[-3000:] + res.stderr[-6000:]

@@ -265,3 +265,107 @@ def test_train_step_with_channels_last_weights_matches_plain_loop():
             assert int(ba) == int(bb) == len(batches), name
         else:
             assert _rel(ba, bb) < 2e-3, name
+
+
+def test_compression_error_matches_upstream_package():
+    """The native path against the UNMODIFIED upstream package (installed under baseline/_ref) on
+    the same device: outputs and residuals agree, and the compression error (norm of what is left
+    in the gradients) agrees to 1e-5 relative - including row pitches of 27 and 650 floats."""
+    from conftest import reference_library
+
+    ref = reference_library()
+    if ref is None:
+        pytest.skip("upstream package not installed under baseline/_ref")
+    dev = torch.device("cuda:0")
+    shapes = [(64, 3, 3, 3), (64, 64, 3, 3), (64, 64, 3, 3), (130, 650), (300, 1200), (10, 512), (16,), (2600, 650)]
+    params = [torch.zeros(s, device=dev) for s in shapes]
+    cfg = dict(rank=2, min_compression_rate=2, num_iters_per_step=2, start_compressing_after_num_steps=0)
+    ours = PowerSGD(params, Config(**cfg), backend="native")
+    theirs = ref.PowerSGD(params, ref.Config(**cfg))
+    # same warm start: both draw from a device generator seeded 0, in the same order
+    assert torch.equal(ours._powersgd._ps_buffer, theirs._powersgd._ps_buffer)
+    ga = _lowrank_grads(shapes, dev, 21)
+    gb = [g.clone() for g in ga]
+    for step in range(3):
+        oa = [o.clone() for o in ours.aggregate(ga)]
+        ob = theirs.aggregate(gb)
+        for x, y, keep in zip(oa, ob, ours.is_compressed_mask):
+            assert _rel(x, y) < 5e-5 or float(y.norm()) == 0.0, (step, tuple(x.shape), _rel(x, y))
+        for x, y, keep in zip(ga, gb, ours.is_compressed_mask):
+            if keep:
+                gap = abs(x.double().norm().item() - y.double().norm().item())
+                assert gap <= 1e-5 * y.double().norm().item(), (step, tuple(x.shape), gap)
+        fresh = _lowrank_grads(shapes, dev, 200 + step)
+        for x, y, f in zip(ga, gb, fresh):
+            x.add_(f)
+            y.add_(f)
+
+
+def test_scratch_garbage_never_reaches_an_output():
+    """NaN canaries: every scratch buffer the kernels use between launches (partial sums of split
+    tiles, orthonormalisation partials, summed-factor copies, the output arena) is filled with NaN
+    before a step; a kernel that read a word it had not written this step would leak one."""
+    dev = torch.device("cuda:0")
+    params = [torch.zeros(s, device=dev) for s in SHAPES]
+    core = BasicPowerSGD(params, BasicConfig(rank=4, num_iters_per_step=2), backend="native")
+    g = _lowrank_grads(SHAPES, dev, 9)
+    core.aggregate(g)  # binds and allocates
+    nat = core._native
+    for buf in [nat._partial, nat._partial_tc, nat._orth_part, nat._orth_rinv, nat._out_arena] + nat.h_loc + nat.h_in:
+        buf.fill_(float("nan"))
+    g = _lowrank_grads(SHAPES, dev, 10)
+    keep = [x.clone() for x in g]
+    out = core.aggregate(g)
+    for o, res, k in zip(out, g, keep):
+        assert torch.isfinite(o).all() and torch.isfinite(res).all()
+        assert _rel(o + res, k) < 1e-6
+    assert torch.isfinite(core._ps_buffer).all() and torch.isfinite(core._qs_buffer).all()
+
+
+def test_single_worker_launch_count_and_warm_start_written_by_the_product():
+    """One worker, rank 2 x 2 iterations: orth (2) + product + orth (2) + product + decompression;
+    the product launch itself leaves the fresh factor in the warm-start buffer (no copy)."""
+    dev = torch.device("cuda:0")
+    shapes = [(64, 3, 3, 3), (64, 64, 3, 3), (130, 650), (256, 512)]  # access widths 1, 4, 2, 4 in ONE launch each
+    params = [torch.zeros(s, device=dev) for s in shapes]
+    core = BasicPowerSGD(params, BasicConfig(rank=2, num_iters_per_step=2), backend="native")
+    g = _lowrank_grads(shapes, dev, 1)
+    core.aggregate(g)
+    nat = core._native
+    assert nat.launches == 7, nat.launches
+    widths = sorted({int(t["vec"]) for t in nat._tile_arrays["nt"]["f"]})
+    assert widths == [1, 2, 4], widths
+    # second half-iteration (right side) wrote P: the warm-start buffer equals the local factor
+    assert torch.equal(core._ps_buffer, nat.h_loc[1][: core._ps_buffer.numel()])
+
+
+def test_a_set_status_word_stops_the_next_training_step():
+    """Failure detection is wired into the training step: when a bounded device-side wait gave up
+    during an earlier step (here the host sets the status word the kernels would have set), the
+    next step raises instead of training on with zeros in place of a peer's contribution."""
+    from powersgd_b200.engine import TrainStep
+    from powersgd_b200.parallel.symm import PowerSGDCommTimeout
+
+    dev = torch.device("cuda:0")
+    torch.manual_seed(3)
+    model = torch.nn.Sequential(torch.nn.Linear(64, 96), torch.nn.ReLU(), torch.nn.Linear(96, 10)).to(dev)
+    params = list(model.parameters())
+    opt = torch.optim.SGD(params, lr=0.05, momentum=0.9)
+    agg = PowerSGD(params, Config(rank=2, min_compression_rate=2, start_compressing_after_num_steps=0))
+    step = TrainStep(model, torch.nn.functional.cross_entropy, opt, agg, cuda_graph=True)
+    x, y = torch.randn(16, 64, device=dev), torch.randint(0, 10, (16,), device=dev)
+    for _ in range(5):
+        step(x, y)
+    assert step._graphs
+    native = agg._powersgd._native
+    native._status.set(3)
+    with pytest.raises(PowerSGDCommTimeout, match="training step 5"):
+        step(x, y)
+    native._status.set(0)
+    step(x, y)  # cleared: training goes on, the device was never involved
+    torch.cuda.synchronize()
+    # the eager entry point looks as well
+    native._status.set(3)
+    with pytest.raises(PowerSGDCommTimeout):
+        optimizer_step(opt, agg)
+    native._status.set(0)

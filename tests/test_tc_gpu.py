@@ -43,14 +43,48 @@ def test_tensor_core_products_match_torch_path(monkeypatch, rank, iters, precisi
         ob = oracle.aggregate(gb)
         torch.cuda.synchronize()
         assert ours._native.uses_tensor_cores
-        assert int(ours._native._tc_status.item()) == 0, "a bounded wait inside the tensor-core kernel ran out"
+        assert ours._native._status.value == 0, "a bounded wait inside the tensor-core kernel ran out"
         for x, y, b, res in zip(oa, ob, before, ga):
             assert torch.isfinite(x).all()
             assert _rel(x, y) < tol, (step, tuple(x.shape), _rel(x, y))
             assert _rel(x + res, b) < 1e-6
         for x, y in zip(ga, gb):
             assert _rel(x, y) < tol, (step, tuple(x.shape), _rel(x, y))
+            if precision == "split":
+                # the compression error itself (norm of the residual) agrees to 1e-5 relative
+                gap = abs(x.double().norm().item() - y.double().norm().item())
+                assert gap <= (1e-5 if rank <= 8 else 1e-4) * y.double().norm().item(), (step, tuple(x.shape), gap)
         fresh = _grads(SHAPES, dev, 50 + step)
+        for x, y, f in zip(ga, gb, fresh):
+            x.add_(f)
+            y.add_(f)
+
+
+def test_long_accumulation_chains_keep_float32_accuracy(monkeypatch):
+    """50 257 rows: every output of `M^T P` sums over chains far longer than one TMEM accumulation
+    segment (512 rows), so the hand-over between the two accumulators and the FP32 running sum are
+    what is under test. Compression error within 1e-5 relative of the float32 formulation."""
+    monkeypatch.setenv("PSGD_B200_GEMM", "tc")
+    monkeypatch.setenv("PSGD_B200_TC_PRECISION", "split")
+    dev = torch.device("cuda:0")
+    shapes = [(50257, 128), (4096, 256)]
+    params = [torch.zeros(s, device=dev) for s in shapes]
+    cfg = BasicConfig(rank=4, num_iters_per_step=2)
+    ours = BasicPowerSGD(params, cfg, backend="native")
+    oracle = BasicPowerSGD(params, cfg, backend="torch")
+    ga = _grads(shapes, dev, 7)
+    gb = [g.clone() for g in ga]
+    for step in range(2):
+        oa = [o.clone() for o in ours.aggregate(ga)]
+        ob = oracle.aggregate(gb)
+        torch.cuda.synchronize()
+        assert ours._native.uses_tensor_cores and ours._native._status.value == 0
+        for x, y in zip(oa, ob):
+            assert _rel(x, y) < 1e-4, (step, tuple(x.shape), _rel(x, y))
+        for x, y in zip(ga, gb):
+            gap = abs(x.double().norm().item() - y.double().norm().item())
+            assert gap <= 1e-5 * y.double().norm().item(), (step, tuple(x.shape), gap)
+        fresh = _grads(shapes, dev, 70 + step)
         for x, y, f in zip(ga, gb, fresh):
             x.add_(f)
             y.add_(f)
@@ -97,7 +131,7 @@ def test_tensor_core_fused_sgd_matches_torch_optimizer(monkeypatch):
         torch.cuda.synchronize()
         native = pa._powersgd._native
         assert native.uses_tensor_cores and native._tiles_dev["fin"]["tc"][1] > 0
-        assert int(native._tc_status.item()) == 0
+        assert native._status.value == 0
         for p, q in zip(ma.parameters(), mb.parameters()):
             assert _rel(p.detach(), q.detach()) < 1e-5, step
             assert _rel(p.grad, q.grad) < 5e-5 or q.grad.norm() == 0, step

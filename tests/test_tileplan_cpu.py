@@ -29,17 +29,19 @@ def test_tiles_cover_every_matrix_exactly_once(rank, tc):
     tiles.fin_rows = 96
     nmat = len(tiles.mats)
     tc_flags = [tc and plan.groups[gi].m % 4 == 0 for gi, _p, _i in tiles.mats]
-    arrays = tiles.build([True] * nmat, tc_flags)
+    widths = [4 if plan.groups[gi].m % 4 == 0 else 2 if plan.groups[gi].m % 2 == 0 else 1 for gi, _p, _i in tiles.mats]
+    arrays = tiles.build(widths, tc_flags)
     for name in ("nt", "nn", "fin"):
         cover = [np.zeros((plan.groups[gi].n, plan.groups[gi].m), dtype=np.int32) for gi, _p, _i in tiles.mats]
-        for key in (4, 1, "tc"):
+        for key in ("f", "tc"):
             for t in arrays[name][key]:
+                assert int(t["vec"]) == widths[int(t["mat"])]
                 cover[t["mat"]][t["row0"] : t["row0"] + t["rows"], t["col0"] : t["col0"] + t["cols"]] += 1
         for c in cover:
             assert (c == 1).all(), name
     # split tiles of one output block share a ticket and occupy consecutive partial-sum slots
     for name in ("nt", "nn"):
-        for key in (4, 1, "tc"):
+        for key in ("f", "tc"):
             by_ticket = {}
             for t in arrays[name][key]:
                 by_ticket.setdefault(int(t["ticket"]), []).append(t)

@@ -27,13 +27,13 @@ def _regular_entry_point(lib, M, P, r):
     n, m = M.shape
     plan = CompressionPlan.build([(n, m)], rank=r)
     tiles = TilePlan(plan, lib)
-    vec = m % 4 == 0 and M.data_ptr() % 16 == 0
+    vec = 4 if (m % 4 == 0 and M.data_ptr() % 16 == 0) else 2 if (m % 2 == 0 and M.data_ptr() % 8 == 0) else 1
     arrays = tiles.build([vec])
     desc = np.zeros(1, dtype=layout.MAT_DTYPE)
     desc["grad"] = M.data_ptr()
     desc["n"], desc["m"], desc["r"] = n, m, r
     desc_dev = _to_device(desc, M.device)
-    tile_arr = arrays["nt"][4 if vec else 1]
+    tile_arr = arrays["nt"]["f"]
     tile_dev = _to_device(tile_arr, M.device)
     partial = torch.empty(tiles.partial_floats, device=M.device)
     tickets = torch.zeros(tiles.n_tickets, dtype=torch.int32, device=M.device)
@@ -41,8 +41,8 @@ def _regular_entry_point(lib, M, P, r):
     null = ctypes.c_void_p(0)
     empty = (ctypes.c_void_p * 1)()
     code = lib.psgd_gemm_ffma_launch(
-        1, 1 if vec else 0, r, ctypes.c_void_p(desc_dev.data_ptr()), ctypes.c_void_p(tile_dev.data_ptr()), len(tile_arr),
-        ctypes.c_void_p(P.data_ptr()), ctypes.c_void_p(Q.data_ptr()), 0, ctypes.cast(empty, ctypes.c_void_p),
+        1, r, ctypes.c_void_p(desc_dev.data_ptr()), ctypes.c_void_p(tile_dev.data_ptr()), len(tile_arr),
+        ctypes.c_void_p(P.data_ptr()), ctypes.c_void_p(Q.data_ptr()), null, 0, ctypes.cast(empty, ctypes.c_void_p),
         ctypes.cast(empty, ctypes.c_void_p), ctypes.c_void_p(partial.data_ptr()), ctypes.c_void_p(tickets.data_ptr()),
         null, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
     )
@@ -63,8 +63,10 @@ def test_noalloc_product_matches_regular_entry_point_twice_in_a_row():
     torch.cuda.set_device(dev)
     gen = torch.Generator(device="cpu").manual_seed(7)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    # two different problems back to back: split over several row blocks, odd pitch, rank 3 -> padded
-    for n, m, r in [(1000, 650, 4), (777, 1301, 3)]:
+    # different problems back to back: split over several row blocks, odd pitch, rank 3 -> padded;
+    # 16-byte rows with one row block (no scratch needed), ranks 1 / 2 / 8, and a shape that fills
+    # the built-in scratch exactly (2^20 floats: 4 column blocks x 256 row blocks x 128 x 8)
+    for n, m, r in [(1000, 650, 4), (777, 1301, 3), (200, 512, 8), (1000, 512, 1), (300, 130, 2), (65536, 512, 8)]:
         M = torch.randn(n, m, generator=gen).to(dev)
         P = torch.randn(n, r, generator=gen).to(dev)
         Q = torch.full((m, r), float("nan"), device=dev)
