@@ -186,7 +186,15 @@ def build_reference(device):
     class Step:
         launches_per_step = 0
         time_aggregate = False   # switched on for the separate aggregate-timing pass only
-        aggregate_ms = None
+        _pair = None
+
+        @property
+        def aggregate_ms(self):
+            if self._pair is None:
+                return None
+            a, b = self._pair
+            b.synchronize()
+            return a.elapsed_time(b)
 
         def __call__(self, x, y):
             loss = torch.nn.functional.cross_entropy(model(x), y)
@@ -196,8 +204,7 @@ def build_reference(device):
                 a.record()
                 ref.optimizer_step(optimizer, aggregator)
                 b.record()
-                b.synchronize()
-                self.aggregate_ms = a.elapsed_time(b)
+                self._pair = (a, b)
             else:
                 ref.optimizer_step(optimizer, aggregator)
             return loss.detach()
@@ -303,12 +310,18 @@ def main():
     clocks = sampler.stop()
 
     # ---- compress + reduce + update time per step, steady state (outside both timed regions) ----
-    agg_steps = max(10, min(100, args.steps))
+    # Bursts of steps enqueued back to back (no host synchronisation inside a burst, so the ranks'
+    # GPUs stay coupled as they are in training); the event pair of the LAST step of every burst
+    # is read after the burst.
+    bursts, burst_len = 20, 10
     if args.impl == "reference":
         step.time_aggregate = True
     agg_samples = []
-    for i in range(agg_steps):
-        step(xs_dev[i % n_slots], ys_dev[i % n_slots])
+    k = 0
+    for _ in range(bursts):
+        for _ in range(burst_len):
+            step(xs_dev[k % n_slots], ys_dev[k % n_slots])
+            k += 1
         torch.cuda.synchronize()
         ms = step.aggregate_ms
         if ms is not None:
@@ -359,8 +372,8 @@ def main():
             "gpu_launches": launches,
             "aggregate_ms_per_step": agg_ms,
             "aggregate_how": (
-                f"device time from the end of backward to the end of the parameter update, mean of {len(agg_samples)} "
-                "steady-state steps after the timed regions, max over ranks; "
+                f"device time from the end of backward to the end of the parameter update: last step of each of "
+                f"{len(agg_samples)} bursts of {burst_len} back-to-back steps after the timed regions, mean, max over ranks; "
                 + ("event-record nodes inside the replayed CUDA graph" if args.impl == "ours" and not args.no_graph
                    else "CUDA-event pair around the aggregation + optimizer call")
             ),

@@ -12,7 +12,8 @@ import os
 from typing import Optional
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_HERE), "csrc", "libpsgd_b200.so")
+# PSGD_B200_LIB points at another build of the same library (e.g. one with development counters)
+LIB_PATH = os.environ.get("PSGD_B200_LIB") or os.path.join(os.path.dirname(_HERE), "csrc", "libpsgd_b200.so")
 
 _lib: Optional[ctypes.CDLL] = None
 _err: Optional[str] = None
