@@ -39,6 +39,12 @@ struct FinalizeArgs {
   int poll_left;
   float* sum_out1;
   float* sum_out2;
+  float sum_scale;   // factor applied to what goes to sum_out2 (1/W keeps the MEAN factor as warm start)
+  // bit 0: the residual is M - update (error against the GLOBAL mean product, as the research
+  //        harness' rank-k reducer defines its memory) instead of M - (local product);
+  // bit 1: the residual is written to the `param` slot of the descriptor (a separate memory
+  //        tensor) and the gradient is left untouched. Only without the fused optimizer step.
+  int flags;
 };
 
 // Column ownership of a lane inside a 128-column block, by access width (see lowrank_ffma.cu).
@@ -201,11 +207,11 @@ __device__ __forceinline__ void finalize_general_tile(const FinalizeArgs& a, con
     if (mom) fin_load4<VEC>(mt.mom + rowoff, lane, t.cols, mv);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      gv[c] -= accE[u][c];
       av[c] = accA[u][c] * a.inv_world;
+      gv[c] -= (a.flags & 1) ? av[c] : accE[u][c];
       if (sgd) psgd_sgd_update(av[c], pv[c], &mv[c], h);
     }
-    fin_store4<VEC>(mt.grad + rowoff, lane, t.cols, gv);
+    fin_store4<VEC>(((a.flags & 2) ? mt.param : mt.grad) + rowoff, lane, t.cols, gv);
     if (sgd) {
       fin_store4<VEC>(mt.param + rowoff, lane, t.cols, pv);
       if (mom) fin_store4<VEC>(mt.mom + rowoff, lane, t.cols, mv);
@@ -287,7 +293,7 @@ __device__ __forceinline__ void finalize_strip_tile(const FinalizeArgs& a, const
           sRs[(h * r + j) * FIN_COLS + fin_panel_pos<VEC>(lc)] = v;
           if (writer) {
             a.sum_out1[base + e] = v;
-            if (a.sum_out2) a.sum_out2[base + e] = v;
+            if (a.sum_out2) a.sum_out2[base + e] = v * a.sum_scale;
           }
         });
       }
@@ -309,7 +315,7 @@ __device__ __forceinline__ void finalize_strip_tile(const FinalizeArgs& a, const
           sLs[(h * r + j) * tile_rows + lr] = v;
           if (writer) {
             a.sum_out1[base + e] = v;
-            if (a.sum_out2) a.sum_out2[base + e] = v;
+            if (a.sum_out2) a.sum_out2[base + e] = v * a.sum_scale;
           }
         });
       }
@@ -320,6 +326,8 @@ __device__ __forceinline__ void finalize_strip_tile(const FinalizeArgs& a, const
   const PsgdHyper hy = a.hyper[mt.hyper];
   const bool sgd = a.fused_sgd != 0;
   const bool mom = sgd && hy.has_momentum;
+  const bool global_res = (a.flags & 1) != 0;
+  float* const res_base = (a.flags & 2) ? mt.param : mt.grad;
 
   for (int rc = 0; rc < t.rows; rc += FIN_ROWS) {
     // ---- global loads of this chunk first ----
@@ -369,11 +377,11 @@ __device__ __forceinline__ void finalize_strip_tile(const FinalizeArgs& a, const
       __align__(16) float av[4];
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) {
-        g4[u][c4] -= accE[u][c4];
         av[c4] = (SAME ? accE[u][c4] : accA[u][c4]) * a.inv_world;
+        g4[u][c4] -= global_res ? av[c4] : accE[u][c4];
         if (sgd) psgd_sgd_update(av[c4], p4[u][c4], &m4[u][c4], hy);
       }
-      fin_store4<VEC>(mt.grad + rowoff, lane, t.cols, g4[u]);
+      fin_store4<VEC>(res_base + rowoff, lane, t.cols, g4[u]);
       if (sgd) {
         fin_store4<VEC>(mt.param + rowoff, lane, t.cols, p4[u]);
         if (mom) fin_store4<VEC>(mt.mom + rowoff, lane, t.cols, m4[u]);
@@ -425,12 +433,13 @@ PSGD_API int psgd_finalize_uses_strip(int nhist, int max_r, int tile_rows, int s
 // tile_rows: height of the tallest tile in `tiles` (a multiple of 32); max_r: largest rank of a
 // matrix in `mats`. With nhist * max_r <= 32 and panels that fit shared memory the strip kernel
 // runs, else the general one. Every tile carries its matrix's access width (`vec`).
-// comm / poll_left / sum_out1 / sum_out2: see FinalizeArgs (comm null: nothing is gathered).
+// comm / poll_left / sum_out1 / sum_out2 / flags / sum_scale: see FinalizeArgs (comm null: nothing
+// is gathered; flags 0 and sum_scale 1 for the library's own step).
 PSGD_API int psgd_finalize_launch(const void* mats, const void* tiles, int ntiles, int tile_rows, int max_r,
                                   const void* hyper, int nhist, const float* const* lloc, const float* const* rloc,
                                   const float* const* lsum, const float* const* rsum, float inv_world,
                                   int fused_sgd, const void* comm, int poll_left, float* sum_out1, float* sum_out2,
-                                  cudaStream_t stream) {
+                                  int flags, float sum_scale, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
   if (tile_rows <= 0 || tile_rows % FIN_ROWS != 0 || max_r <= 0) {
     psgd_set_error("psgd_finalize_launch: tile_rows=%d must be a positive multiple of %d, max_r=%d positive", tile_rows, FIN_ROWS, max_r);
@@ -457,6 +466,12 @@ PSGD_API int psgd_finalize_launch(const void* mats, const void* tiles, int ntile
   a.poll_left = poll_left;
   a.sum_out1 = sum_out1;
   a.sum_out2 = sum_out2;
+  a.flags = flags;
+  a.sum_scale = sum_scale;
+  if (flags != 0 && fused_sgd) {
+    psgd_set_error("psgd_finalize_launch: residual flags %d cannot be combined with the fused optimizer step", flags);
+    return -1;
+  }
   bool same = true;
   for (int i = 0; i < nhist; ++i) same = same && lloc[i] == lsum[i] && rloc[i] == rsum[i];
   const bool strip = finalize_takes_strip(nhist, max_r, tile_rows, same);
@@ -502,6 +517,7 @@ struct FlatArgs {
              // 12: wait for the gathered chunks this block reads, then unpack ; 13: same + SGD
   const PsgdCommDev* comm;
   long long n_pad;  // modes 12, 13: length of the arena's data region (whole chunks per rank)
+  int keep;         // packing modes: leave the inputs as they are instead of zeroing them
 };
 
 constexpr int FLAT_THREADS = 256;
@@ -547,11 +563,11 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
       continue;
     } else if (mode == 0) {
       a.flat[it.flat_off + i] = it.grad[i] / a.divisor;
-      it.grad[i] = 0.f;
+      if (!a.keep) it.grad[i] = 0.f;
       continue;
     } else if (mode == 5) {
       const float v = it.grad[i] / a.divisor;
-      it.grad[i] = 0.f;
+      if (!a.keep) it.grad[i] = 0.f;
       for (int p = 0; p < c.world; ++p) psgd_comm_store(psgd_comm_slot(c, p, e1, c.rank) + it.flat_off + i, v, e1);
       continue;
     } else if (mode == 1 || mode == 2) {
@@ -562,7 +578,7 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
       g = psgd_comm_reduce(c, e1, it.flat_off + i, ok);
     } else {
       g = it.grad[i] / a.divisor;
-      it.grad[i] = 0.f;
+      if (!a.keep) it.grad[i] = 0.f;
     }
     if (mode == 2 || mode == 4 || mode == 7 || mode == 13) {
       float p = it.param[i];
@@ -588,7 +604,7 @@ __device__ __forceinline__ void flat_one(const FlatArgs& a, const PsgdFlat& it, 
     return;
   } else if (MODE == 0) {
     a.flat[it.flat_off + i] = it.grad[i] / a.divisor;
-    it.grad[i] = 0.f;
+    if (!a.keep) it.grad[i] = 0.f;
     return;
   } else if (MODE == 1 || MODE == 2) {
     g = a.flat[it.flat_off + i];
@@ -596,7 +612,7 @@ __device__ __forceinline__ void flat_one(const FlatArgs& a, const PsgdFlat& it, 
     g = __ldcg(a.flat + it.flat_off + i);
   } else {
     g = it.grad[i] / a.divisor;
-    it.grad[i] = 0.f;
+    if (!a.keep) it.grad[i] = 0.f;
   }
   if (MODE == 2 || MODE == 4 || MODE == 13) {
     float p = it.param[i];
@@ -622,7 +638,7 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_vec_kernel(FlatArgs a)
     for (int e = threadIdx.x; e < left; e += FLAT_THREADS) {
       const long long i = first + e;
       const float v = it.grad[i] / a.divisor;
-      it.grad[i] = 0.f;
+      if (!a.keep) it.grad[i] = 0.f;
       for (int p = 0; p < cc.world; ++p) psgd_comm_store(psgd_comm_slot(cc, p, ep, cc.rank) + it.flat_off + i, v, ep);
     }
     return;
@@ -661,7 +677,7 @@ __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_vec_kernel(FlatArgs a)
       // the scalar path divides; a multiplication by the reciprocal differs in the last bit for
       // divisors that are not powers of two, so divide here too
       g.x /= a.divisor; g.y /= a.divisor; g.z /= a.divisor; g.w /= a.divisor;
-      *grad4 = zero4;
+      if (!a.keep) *grad4 = zero4;
       if (MODE == 0) {
         *flat4 = g;
         continue;
@@ -707,9 +723,10 @@ static void flat_vec_launch(const FlatArgs& a, int nblocks, cudaStream_t stream)
 // vec != 0 promises 16-byte aligned grad / param / mom / out pointers and flat offsets that are
 // multiples of four floats; modes 5-7 (flag-in-data words) always run element-wise, and so do the
 // op-5 items of a mixed launch (mode 9), whose pointers need no alignment.
+// keep != 0: the packing modes (0, 3, 4, 5 and the op-5 items of mode 9) leave their inputs untouched.
 PSGD_API int psgd_flat_launch(int mode, int vec, const void* items, const int* block_item, const int* block_first,
                               int nblocks, const void* hyper, float* flat, float divisor, const void* comm,
-                              long long n_pad, cudaStream_t stream) {
+                              long long n_pad, int keep, cudaStream_t stream) {
   if (nblocks <= 0) return 0;
   if (mode >= 5 && mode != 8 && comm == nullptr) {
     psgd_set_error("psgd_flat_launch: mode %d needs a communication channel", mode);
@@ -729,6 +746,7 @@ PSGD_API int psgd_flat_launch(int mode, int vec, const void* items, const int* b
   a.mode = mode;
   a.comm = (const PsgdCommDev*)comm;
   a.n_pad = n_pad;
+  a.keep = keep;
   if (vec && !(mode >= 5 && mode <= 7)) {
     switch (mode) {
       case 0: flat_vec_launch<0>(a, nblocks, stream); break;

@@ -349,23 +349,27 @@ class NativeCompressor:
         moms: Optional[Sequence[Optional[torch.Tensor]]] = None,
         hyper_index: Optional[Sequence[int]] = None,
         need_out: bool = True,
+        outs: Optional[Sequence[torch.Tensor]] = None,
     ) -> None:
+        """`outs`: caller-owned tensors (laid out like the gradients) that receive the averaged
+        update instead of this object's own arena."""
         key = (
             tuple(g.data_ptr() for g in grads),
             None if params is None else tuple(p.data_ptr() for p in params),
             None if moms is None else tuple(0 if m is None else m.data_ptr() for m in moms),
             need_out,
+            None if outs is None else tuple(o.data_ptr() for o in outs),
         )
         if key == self._key:
             return
         for g in grads:
             if not is_dense(g) or g.dtype != torch.float32 or g.device != self.device:
                 raise ValueError("native PowerSGD needs dense float32 gradients on its device")
-        for name, others in (("parameters", params), ("momentum buffers", moms)):
+        for name, others in (("parameters", params), ("momentum buffers", moms), ("outputs", outs)):
             for g, o in zip(grads, others or []):
                 if o is not None and not same_layout(o, g):
                     raise ValueError(f"native PowerSGD needs {name} laid out like their gradients")
-        if need_out and self._out_arena is None:
+        if need_out and outs is None and self._out_arena is None:
             self._out_arena = torch.empty(self.tiles.total_elems, device=self.device, dtype=torch.float32)
         where = self.plan.locate()
         descs = np.zeros(len(self.tiles.mats), dtype=layout.MAT_DTYPE)
@@ -383,7 +387,10 @@ class NativeCompressor:
             d["grad"] = grads[idx].data_ptr()
             d["param"] = 0 if params is None else params[idx].data_ptr()
             d["mom"] = 0 if (moms is None or moms[idx] is None) else moms[idx].data_ptr()
-            if need_out:
+            if need_out and outs is not None:
+                out_views[idx] = outs[idx]
+                d["out"] = outs[idx].data_ptr()
+            elif need_out:
                 view = self._out_arena[out_offsets[idx] : out_offsets[idx] + grads[idx].numel()]
                 out_views[idx] = like_strided(view, grads[idx])
                 d["out"] = view.data_ptr()
@@ -521,9 +528,13 @@ class NativeCompressor:
             return False
         return bool(self.lib.psgd_finalize_uses_strip(self.T, self.tiles.max_r, self.tiles.fin_rows, 0))
 
-    def _finalize(self, sides: List[bool], fused_sgd: bool, workers: int, gather_state: Optional[torch.Tensor] = None):
+    def _finalize(self, sides: List[bool], fused_sgd: bool, workers: int, gather_state: Optional[torch.Tensor] = None,
+                  flags: int = 0):
         """`gather_state`: the warm-start buffer that receives the summed factor of the last
-        half-iteration when this launch is also its consumer (see `_gathers_in_finalize`)."""
+        half-iteration when this launch is also its consumer (see `_gathers_in_finalize`).
+        `flags`: residual options of the strip / general kernels (csrc/finalize.cu, FinalizeArgs)."""
+        if flags and self._tiles_dev["fin"]["tc"][1]:
+            raise ValueError("residual options are not available with the tensor-core decompression kernel")
         lloc, rloc, lsum, rsum = [], [], [], []
         for t, left in enumerate(sides):
             if left:
@@ -574,6 +585,8 @@ class NativeCompressor:
                 0 if sides[-1] else 1,  # last half-iteration left: the fresh (summed) factor is the right one
                 _ptr(self.h_sum[len(sides) - 1]) if gather else ctypes.c_void_p(0),
                 _ptr(gather_state) if gather else ctypes.c_void_p(0),
+                int(flags),
+                1.0,
                 _stream_ptr(),
             )
             native.check(code, "psgd_finalize_launch")
@@ -745,18 +758,20 @@ class NativeFlatAllReduce:
         self.n_pad = 0
         self._bulk_layout = None
         self._pushed = False  # one-shot path: this step's pack + push already left with another launch
+        self._keep_inputs = False
 
     def check(self) -> None:
         """Raise `PowerSGDCommTimeout` if a bounded wait of an earlier launch gave up."""
         if self.comm is not None:
             self.comm.check()
 
-    def _bind(self, grads, params=None, moms=None, hyper_index=None, need_out=True):
+    def _bind(self, grads, params=None, moms=None, hyper_index=None, need_out=True, outs=None):
         key = (
             tuple(g.data_ptr() for g in grads),
             None if params is None else tuple(p.data_ptr() for p in params),
             None if moms is None else tuple(0 if m is None else m.data_ptr() for m in moms),
             need_out,
+            None if outs is None else tuple(o.data_ptr() for o in outs),
         )
         if key == self._key:
             return
@@ -764,7 +779,7 @@ class NativeFlatAllReduce:
         # every tensor starts at a multiple of four floats in the flat buffer (16-byte accesses)
         total = sum(-(-g.numel() // 4) * 4 for g in grads)
         self._flat = torch.zeros(total, device=device, dtype=torch.float32)
-        self._out = torch.empty(total, device=device, dtype=torch.float32) if need_out else None
+        self._out = torch.empty(total, device=device, dtype=torch.float32) if (need_out and outs is None) else None
         items = np.zeros(len(grads), dtype=layout.FLAT_DTYPE)
         per_block = self.lib.psgd_flat_block_elems()
         block_item, block_first = [], []
@@ -772,14 +787,18 @@ class NativeFlatAllReduce:
         for i, g in enumerate(grads):
             if not is_dense(g) or g.dtype != torch.float32:
                 raise ValueError("native flat all-reduce needs dense float32 tensors")
-            for o in ((params[i] if params is not None else None), (moms[i] if moms is not None else None)):
+            for o in ((params[i] if params is not None else None), (moms[i] if moms is not None else None),
+                      (outs[i] if outs is not None else None)):
                 if o is not None and not same_layout(o, g):
-                    raise ValueError("native flat all-reduce needs parameters and momentum buffers laid out like the gradients")
+                    raise ValueError("native flat all-reduce needs parameters, momentum buffers and outputs laid out like the gradients")
             it = items[i]
             it["grad"] = g.data_ptr()
             it["param"] = 0 if params is None else params[i].data_ptr()
             it["mom"] = 0 if (moms is None or moms[i] is None) else moms[i].data_ptr()
-            if need_out:
+            if need_out and outs is not None:
+                views.append(outs[i])
+                it["out"] = outs[i].data_ptr()
+            elif need_out:
                 v = self._out[cursor : cursor + g.numel()]
                 views.append(like_strided(v, g))
                 it["out"] = v.data_ptr()
@@ -852,6 +871,7 @@ class NativeFlatAllReduce:
             float(divisor),
             self.comm.ptr if self.comm is not None else ctypes.c_void_p(0),
             ctypes.c_longlong(self.n_pad),
+            1 if self._keep_inputs else 0,
             _stream_ptr(),
         )
         native.check(code, "psgd_flat_launch")
@@ -877,11 +897,18 @@ class NativeFlatAllReduce:
             dist.all_reduce(self._flat)
             self._launch(2 if sgd else 1, hyper_dev, 1.0)
 
-    def aggregate(self, gradients: List[torch.Tensor]) -> List[torch.Tensor]:
+    def aggregate(self, gradients: List[torch.Tensor], outs: Optional[Sequence[torch.Tensor]] = None,
+                  keep_inputs: bool = False) -> List[torch.Tensor]:
+        """Mean over workers. `outs`: caller-owned destination tensors (default: views of this
+        object's buffer, valid until the next call). `keep_inputs`: do not zero the inputs."""
         self.check()
         self.launches = 0
-        self._bind(gradients)
-        self._run(self._hyper_dev, world_size(), sgd=False)
+        self._bind(gradients, outs=outs)
+        self._keep_inputs = bool(keep_inputs)
+        try:
+            self._run(self._hyper_dev, world_size(), sgd=False)
+        finally:
+            self._keep_inputs = False
         return list(self._views)
 
     def aggregate_and_step(self, gradients, params, moms, hyper_index, hyper_dev) -> None:
@@ -947,7 +974,7 @@ class MultiTensorAccumulate:
         code = self.lib.psgd_flat_launch(
             8 if push is None else 9, self._vec, _ptr(self._items), _ptr(self._block_item), _ptr(self._block_first),
             self._nblocks, _ptr(self._hyper), ctypes.c_void_p(0), 1.0 if push is None else float(world_size()),
-            ctypes.c_void_p(0) if push is None else push.comm.ptr, ctypes.c_longlong(0), _stream_ptr(),
+            ctypes.c_void_p(0) if push is None else push.comm.ptr, ctypes.c_longlong(0), 0, _stream_ptr(),
         )
         native.check(code, "psgd_flat_launch")
         if push is not None:

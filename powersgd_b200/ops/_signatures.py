@@ -26,14 +26,14 @@ def declare(lib) -> None:
     lib.psgd_gemm_ffma_launch.argtypes = [i32, i32, vp, vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp]
 
     lib.psgd_finalize_launch.restype = i32
-    lib.psgd_finalize_launch.argtypes = [vp, vp, i32, i32, i32, vp, i32, vp, vp, vp, vp, f32, i32, vp, i32, vp, vp, vp]
+    lib.psgd_finalize_launch.argtypes = [vp, vp, i32, i32, i32, vp, i32, vp, vp, vp, vp, f32, i32, vp, i32, vp, vp, i32, f32, vp]
     lib.psgd_finalize_uses_strip.restype = i32
     lib.psgd_finalize_uses_strip.argtypes = [i32, i32, i32, i32]
 
     lib.psgd_flat_block_elems.restype = i32
     lib.psgd_flat_block_elems.argtypes = []
     lib.psgd_flat_launch.restype = i32
-    lib.psgd_flat_launch.argtypes = [i32, i32, vp, vp, vp, i32, vp, vp, f32, vp, C.c_longlong, vp]
+    lib.psgd_flat_launch.argtypes = [i32, i32, vp, vp, vp, i32, vp, vp, f32, vp, C.c_longlong, i32, vp]
 
     for name, sig in _OPTIONAL.items():
         fn = getattr(lib, name, None)

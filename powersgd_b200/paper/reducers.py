@@ -118,14 +118,35 @@ class Reducer:
         raise NotImplementedError
 
 
+def _native_ok(grad_in, grad_out, memory_out) -> bool:
+    """CUDA float32 dense tensors throughout: the reducers below then run on the native kernels."""
+    from . import native_lowrank
+
+    return native_lowrank.usable(list(grad_in) + list(grad_out) + list(memory_out))
+
+
 class ExactReducer(Reducer):
-    """Plain averaging; nothing is lost, so the memories are cleared."""
+    """Plain averaging; nothing is lost, so the memories are cleared. On CUDA tensors the mean
+    runs through this package's peer-store all-reduce kernels (pack with 1/W, one-shot or
+    two-shot exchange, unpack straight into `grad_out`)."""
+
+    _native = None
 
     def reduce(self, grad_in, grad_out, memory_out) -> int:
         with self.timer("reduce.zero_mem", verbosity=2):
-            for mem in memory_out:
-                mem.zero_()
+            if memory_out and memory_out[0].is_cuda:
+                torch._foreach_zero_(list(memory_out))
+            else:
+                for mem in memory_out:
+                    mem.zero_()
         with self.timer("reduce.reduce", verbosity=2):
+            if _native_ok(grad_in, grad_out, memory_out):
+                from ..cuda_path import NativeFlatAllReduce
+
+                if self._native is None:
+                    self._native = NativeFlatAllReduce()
+                self._native.aggregate(list(grad_in), outs=list(grad_out), keep_inputs=True)
+                return 0 if self.n_workers == 1 else 8 * sum(t.nelement() * t.element_size() for t in grad_in)
             return reduce_mean_list(self.device, grad_in, grad_out, self.timer)
 
 
@@ -138,6 +159,23 @@ class _LowRankBase(Reducer):
         self.rank = rank  # note: shadows the worker rank, as the original does
         self.p_memory = None
         self.q_memory = None
+        self._native = None              # native_lowrank.NativeLowRank once CUDA tensors were seen
+        self._native_launches_last = 0   # kernels launched by the last native reduce()
+
+    def _native_driver(self, matrices, iters: int):
+        """Driver of the native path; its factor memories become `p_memory` / `q_memory` (same
+        layout as the original: tensor after tensor)."""
+        from .native_lowrank import NativeLowRank
+
+        fresh = self._native is None
+        if fresh:
+            self._native = NativeLowRank(matrices, self.rank, iters, self.device)
+            self.p_memory, self.q_memory = self._native.p_memory, self._native.q_memory
+        self._native.launches = 0
+        return self._native, fresh
+
+    def _rank1_bits(self, vectors) -> int:
+        return 8 * sum(t.nelement() * t.element_size() for t, _, _ in vectors)
 
     def _views(self, matrices):
         sizes = []
@@ -174,9 +212,24 @@ class RankKReducer(_LowRankBase):
     def set_random(self, vector: torch.Tensor) -> None:
         self._shared_randn_(vector)
 
+    def _reduce_native(self, vectors, matrices) -> int:
+        drv, fresh = self._native_driver(matrices, iters=2)
+        with self.timer("reduce.prepare.q", verbosity=2):
+            if fresh or not self.reuse_query:
+                for i in range(len(matrices)):
+                    self.set_random(drv.core.q_view(i))
+        with self.timer("reduce.rank1", verbosity=2):
+            drv.reduce_vectors(vectors)
+        with self.timer("reduce.lowrank", verbosity=2):
+            drv.rank_k(matrices)
+        self._native_launches_last = drv.launches
+        return n_bits(self.p_memory) + n_bits(self.q_memory) + self._rank1_bits(vectors)
+
     def reduce(self, grad_in, grad_out, memory_out) -> int:
         bits = 0
         vectors, matrices = _split_by_dim(grad_in, grad_out, memory_out)
+        if matrices and _native_ok(grad_in, grad_out, memory_out):
+            return self._reduce_native(vectors, matrices)
         with self.timer("reduce.allocate_memory", verbosity=2):
             ps, qs, fresh = self._views(matrices)
         with self.timer("reduce.prepare.q", verbosity=2):
@@ -227,9 +280,25 @@ class HalfRankKReducer(_LowRankBase):
         self._shared_randn_(vector)
         orthogonalize(vector)
 
+    def _reduce_native(self, vectors, matrices) -> int:
+        drv, fresh = self._native_driver(matrices, iters=1)
+        compute_p = self.next_operation == "p"
+        self.next_operation = "q" if compute_p else "p"
+        if fresh:
+            for i in range(len(matrices)):
+                self.set_random(drv.core.q_view(i))
+        with self.timer("reduce.rank1", verbosity=2):
+            drv.reduce_vectors(vectors)
+        with self.timer("reduce.lowrank", verbosity=2):
+            drv.half_rank_k(matrices, compute_p)
+        self._native_launches_last = drv.launches
+        return n_bits(self.p_memory if compute_p else self.q_memory) + self._rank1_bits(vectors)
+
     def reduce(self, grad_in, grad_out, memory_out) -> int:
         bits = 0
         vectors, matrices = _split_by_dim(grad_in, grad_out, memory_out)
+        if matrices and _native_ok(grad_in, grad_out, memory_out):
+            return self._reduce_native(vectors, matrices)
         with self.timer("reduce.rank1.pack", verbosity=2):
             flat = TensorBuffer([t for t, _, _ in vectors])
         with self.timer("reduce.rank1.all_reduce", verbosity=2):

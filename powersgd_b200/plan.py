@@ -78,11 +78,13 @@ class CompressionPlan:
     q_total: int
 
     @classmethod
-    def build(cls, shapes: Sequence[Sequence[int]], rank: int) -> "CompressionPlan":
-        by_shape: Dict[Tuple[int, int], ShapeGroup] = {}
+    def build(cls, shapes: Sequence[Sequence[int]], rank: int, batch_same_shapes: bool = True) -> "CompressionPlan":
+        """`batch_same_shapes=False` gives every tensor its own group (the research harness' reducers
+        keep one factor pair per tensor; at rank 1 this also means one norm per matrix)."""
+        by_shape: Dict[Tuple, ShapeGroup] = {}
         for idx, shape in enumerate(shapes):
             n, m = matrix_shape(shape)
-            key = (n, m)
+            key = (n, m) if batch_same_shapes else (n, m, idx)
             if key not in by_shape:
                 by_shape[key] = ShapeGroup(n=n, m=m, r=min(int(rank), n, m))
             by_shape[key].members.append(idx)

@@ -266,6 +266,75 @@ def scenario_train_step_graph():
         print("SCENARIO-OK", losses[0], losses[-1])
 
 
+def scenario_reducers_native():
+    """RankK / HalfRankK / Exact reducers of the research harness on the native kernels (factors
+    exchanged by the product kernels' peer pushes) against the unmodified upstream classes on the
+    library all-reduce: outputs, memories and bit counts agree; outputs identical on all ranks."""
+    import importlib.util
+
+    rank, world, dev = _init("nccl")
+    path = os.path.join(ROOT, "baseline", "_ref", "paper_code", "gradient_reducers.py")
+    if not os.path.exists(path):
+        if rank == 0:
+            print("SCENARIO-OK (upstream research code not installed: nothing to compare)")
+        return
+    sys.path.insert(0, os.path.dirname(path))
+    spec = importlib.util.spec_from_file_location("_upstream_reducers", path)
+    up = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(up)
+    import contextlib
+
+    from powersgd_b200.paper import reducers as ours_mod
+
+    class _Timer:
+        def __call__(self, *a, **k):
+            return contextlib.nullcontext()
+
+    shapes = [(64, 3, 3, 3), (64, 64, 3, 3), (130, 650), (300, 1200), (10, 512), (64,), (10,)]
+    for name, kwargs in (("RankKReducer", dict(rank=2, reuse_query=True)), ("HalfRankKReducer", dict(rank=2)), ("ExactReducer", dict())):
+        theirs = getattr(up, name)(random_seed=5, device=dev, timer=_Timer(), **kwargs)
+        # the upstream base class draws a 512 MB table nothing reads, advancing its random stream
+        del theirs.precalc_numbers
+        import numpy as np
+
+        theirs.rng = np.random.RandomState(5)
+        ours = getattr(ours_mod, name)(random_seed=5, device=dev, **kwargs)
+        mem_a = [torch.zeros(s, device=dev) for s in shapes]
+        mem_b = [torch.zeros(s, device=dev) for s in shapes]
+        g = torch.Generator().manual_seed(100 + rank)
+        for step in range(4):
+            grads = []
+            for s in shapes:
+                if len(s) == 1:
+                    grads.append(torch.randn(s, generator=g).to(dev))
+                else:
+                    n = s[0]
+                    m = int(torch.Size(s).numel() // n)
+                    a = torch.randn(n, 5, generator=g) @ torch.randn(5, m, generator=g) + 0.1 * torch.randn(n, m, generator=g)
+                    grads.append(a.view(s).to(dev))
+            send_a = [x + m for x, m in zip(grads, mem_a)]
+            send_b = [x + m for x, m in zip(grads, mem_b)]
+            out_a = [torch.full(s, float("nan"), device=dev) for s in shapes]
+            out_b = [torch.zeros(s, device=dev) for s in shapes]
+            bits_a = ours.reduce(send_a, out_a, mem_a)
+            bits_b = theirs.reduce(send_b, out_b, mem_b)
+            torch.cuda.synchronize()
+            assert bits_a == bits_b, (name, step, bits_a, bits_b)
+            for s, x, y, ma, mb in zip(shapes, out_a, out_b, mem_a, mem_b):
+                assert _rel(x, y) < 3e-5, (name, step, s, _rel(x, y))
+                assert _same_on_all_ranks(x, world), (name, "outputs differ between ranks")
+                if float(mb.norm()) > 0:
+                    assert _rel(ma, mb) < 3e-5, (name, step, s, _rel(ma, mb))
+        native = getattr(ours, "_native", None)
+        assert native is not None, name
+        comm = native.comp.comm if hasattr(native, "comp") else native.comm
+        assert comm is not None, "expected the in-kernel all-reduce path"
+        comm.check()
+        dist.barrier()
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
 def scenario_train_step_timeout():
     """A rank stays away from a training step: the others' bounded device-side waits give up, and
     their NEXT call of the training step raises (naming the step) instead of applying an update
