@@ -316,6 +316,8 @@ class NativeCompressor:
         self._side_stream = torch.cuda.Stream(device=self.device)
         self._early = None  # (side, event) of an orthonormalisation issued by begin_step()
         self._early_launches = 0
+        self._early_bucket: frozenset = frozenset()
+        self._early_product_done = None  # event of a first product launched ahead for the early bucket
         # multi-GPU: factors are all-reduced by the product kernels themselves (peer pushes) plus
         # a small consumer kernel; PSGD_B200_COMM=nccl selects the library all-reduce instead
         self.comm = None
@@ -436,11 +438,56 @@ class NativeCompressor:
             self._tiles_dev[name] = {
                 v: (_to_device(a, self.device) if len(a) else None, len(a)) for v, a in by_vec.items()
             }
+        self._split_tile_lists()
         self._partial = torch.empty(self.tiles.partial_floats, device=self.device, dtype=torch.float32)
         self._partial_tc = torch.empty(self.tiles.partial_tc_floats, device=self.device, dtype=torch.float32)
         self._tickets = torch.zeros(self.tiles.n_tickets, device=self.device, dtype=torch.int32)
         self._out_views = out_views
         self._key = key
+
+    # -- early bucket ---------------------------------------------------------------------
+    def set_early_bucket(self, compressed_indices: Sequence[int]) -> None:
+        """Compressed tensors (positions in the compressed list) whose gradients are complete
+        early in backward: the first product of a step can be launched for them from a
+        post-accumulate hook, on a side stream, while backward is still running for the rest."""
+        self._early_bucket = frozenset(int(i) for i in compressed_indices)
+        if self._key is not None:
+            self._split_tile_lists()
+
+    def _split_tile_lists(self) -> None:
+        """Product tile lists of the early bucket ("fA") and of everything else ("fB")."""
+        early_mats = [mi for mi, (_gi, _pos, idx) in enumerate(self.tiles.mats) if idx in self._early_bucket]
+        for name in ("nt", "nn"):
+            arr = self._tile_arrays[name]["f"]
+            mask = np.isin(arr["mat"], early_mats) if len(arr) else np.zeros(0, dtype=bool)
+            for key, sub in (("fA", arr[mask]), ("fB", arr[~mask])):
+                self._tiles_dev[name][key] = (_to_device(np.ascontiguousarray(sub), self.device) if len(sub) else None, len(sub))
+
+    def early_product(self) -> bool:
+        """Launch the first product of the coming step for the early bucket NOW, on the side
+        stream (after the orthonormalisation `begin_step` issued there). Returns False when there
+        is nothing to launch early. `_half_iterations` then only launches the rest and joins."""
+        if not self._early_bucket or self._early is None or self._key is None:
+            return False
+        core = self.core
+        left = (core.step_counter * self.T) % 2 == 0
+        if self._early[0] != ("p" if left else "q"):
+            return False
+        name = "nt" if left else "nn"
+        if self._tiles_dev[name]["fA"][1] == 0:
+            return False
+        state_out = core._qs_buffer if left else core._ps_buffer
+        fork = torch.cuda.Event()
+        fork.record(torch.cuda.current_stream())
+        self._side_stream.wait_event(fork)
+        with torch.cuda.stream(self._side_stream):
+            before = self.launches
+            self._gemm(left, self.h_in[0], self.h_loc[0], [], self.cmat[0], state_out if world_size() == 1 else None, part="early")
+            self._early_launches += self.launches - before
+            done = torch.cuda.Event()
+            done.record(self._side_stream)
+        self._early_product_done = done
+        return True
 
     # -- phases ----------------------------------------------------------------------------
     def _orth(self, side: str, x: torch.Tensor, copy_to: torch.Tensor, prev: List[torch.Tensor], cm: List[torch.Tensor],
@@ -471,10 +518,12 @@ class NativeCompressor:
         self.launches += 2  # Gram + factorisation, then the application of R^-1
 
     def _gemm(self, transposed: bool, fin: torch.Tensor, fout: torch.Tensor, corr_fac, corr_c,
-              fout2: Optional[torch.Tensor] = None):
+              fout2: Optional[torch.Tensor] = None, part: str = "all"):
+        """`part`: "all", or one half of a split launch - "early" (the CUDA-core tiles of the
+        matrices in the early bucket) / "late" (everything else); see `set_early_bucket`."""
         name = "nt" if transposed else "nn"
         tiles, count = self._tiles_dev[name]["tc"]
-        if count:
+        if count and part != "early":
             code = self.lib.psgd_gemm_tc_launch(
                 1 if transposed else 0,
                 1 if self._tc_split else 0,
@@ -497,7 +546,7 @@ class NativeCompressor:
             )
             native.check(code, "psgd_gemm_tc_launch")
             self.launches += 1
-        tiles, count = self._tiles_dev[name]["f"]
+        tiles, count = self._tiles_dev[name]["f" if part == "all" else ("fA" if part == "early" else "fB")]
         if count:
             code = self.lib.psgd_gemm_ffma_launch(
                 1 if transposed else 0,
@@ -631,7 +680,13 @@ class NativeCompressor:
                     self._orth(side, state_in, self.h_in[t], same, self.cmat[t], gather_to)
             with _Range(f"psgd.iter{t}.product"):
                 # one worker: the product is final, so the kernel also writes the warm-start buffer
-                self._gemm(left, self.h_in[t], self.h_loc[t], other, self.cmat[t], state_out if workers == 1 else None)
+                part = "all"
+                if t == 0 and self._early_product_done is not None:
+                    part = "late"  # the early bucket's tiles were launched during backward
+                self._gemm(left, self.h_in[t], self.h_loc[t], other, self.cmat[t], state_out if workers == 1 else None, part=part)
+                if part == "late":
+                    torch.cuda.current_stream().wait_event(self._early_product_done)
+                    self._early_product_done = None
             total = state_out.numel()
             with _Range(f"psgd.iter{t}.reduce"):
                 if p2p and (t < self.T - 1 or defer_last):

@@ -78,6 +78,21 @@ class TrainStep:
         # residuals detached from p.grad for the duration of backward: (parameter, residual)
         self._held: list = []
         self._accumulate = None
+        # Overlap with the tail of backward: the compressed tensors whose gradients are complete
+        # first (the last layers) form the "early bucket". Their residuals stay in p.grad, so autograd
+        # accumulates onto them as it goes; a post-accumulate hook counts them, and when the bucket
+        # is full its share of the step's first product is launched on the aggregator's side stream
+        # while backward goes on for the earlier layers (in a recorded step: a parallel branch of
+        # the graph). PSGD_B200_OVERLAP=0 switches it off.
+        import os
+
+        self._overlap = os.environ.get("PSGD_B200_OVERLAP", "1") != "0" and self.device.type == "cuda" and grad_clip is None
+        self._hook_order: list = []        # parameter ids in the order their gradients completed (first compressed step)
+        self._hook_recording = False
+        self._bucket: dict = {}            # id(parameter) -> parameter, the early bucket
+        self._bucket_seen = 0
+        self._hooks_installed = False
+        self._bucket_decided = False
 
     # ------------------------------------------------------------------------------------
     def _weights_to_channels_last(self) -> None:
@@ -121,15 +136,79 @@ class TrainStep:
         # (autograd then adopts the fresh gradients without arithmetic) and `_fold` adds all
         # fresh gradients onto their residuals in one launch instead of one add per parameter.
         self._held = []
+        self._bucket_seen = 0
+        self._bucket_live = False
         mask = getattr(self.aggregator, "is_compressed_mask", None)
+        if self._overlap and mask is not None and getattr(self.aggregator, "compressing", False):
+            self._install_hooks()
+            if not self._bucket_decided:
+                self._hook_order = []
+                self._hook_recording = True   # this backward tells in which order gradients complete
         if mask is not None and getattr(self.aggregator, "compressing", False):
             fold = self.device.type == "cuda" and getattr(self.aggregator, "supports_fused_step", lambda _o: False)(self.optimizer)
             for p, keep in zip(self._params(), mask):
                 if not keep:
                     p.grad = None
                 elif fold and p.grad is not None:
+                    if id(p) in self._bucket:
+                        self._bucket_live = True   # stays attached: autograd accumulates onto the residual
+                        continue
                     self._held.append((p, p.grad))
                     p.grad = None
+
+    # -- overlap with backward -------------------------------------------------------------
+    def _install_hooks(self) -> None:
+        if self._hooks_installed or not self._overlap:
+            return
+        mask = getattr(self.aggregator, "is_compressed_mask", None)
+        if mask is None:
+            return
+        self._hooks_installed = True
+        for p, keep in zip(self._params(), mask):
+            if keep:
+                p.register_post_accumulate_grad_hook(self._on_grad_ready)
+
+    def _on_grad_ready(self, p: torch.Tensor) -> None:
+        """Post-accumulate hook of a compressed parameter (fires once per backward per parameter,
+        however many times the parameter is used)."""
+        if self._hook_recording:
+            self._hook_order.append(id(p))
+            return
+        if id(p) in self._bucket and self._bucket_live:
+            self._bucket_seen += 1
+            if self._bucket_seen == len(self._bucket):
+                self._launch_early()
+
+    def _choose_bucket(self) -> None:
+        """Early bucket = the compressed parameters that completed first in the recorded backward,
+        up to ~60 % of the compressed elements (for a ResNet: the last stage and the classifier)."""
+        core = getattr(self.aggregator, "_powersgd", None)
+        native = getattr(core, "_native", None)
+        if native is None or not self._hook_order:
+            return
+        params = self._params()
+        by_id = {id(p): p for p in params}
+        compressed = [p for p, keep in zip(params, self.aggregator.is_compressed_mask) if keep]
+        position = {id(p): i for i, p in enumerate(compressed)}
+        total = sum(p.numel() for p in compressed)
+        picked, acc = [], 0
+        for pid in self._hook_order:
+            if pid not in position or acc >= 0.6 * total:
+                continue
+            picked.append(pid)
+            acc += by_id[pid].numel()
+        if len(picked) == len(compressed) or not picked:
+            return  # nothing would be left for after backward / nothing early: no split
+        self._bucket = {pid: by_id[pid] for pid in picked}
+        native.set_early_bucket([position[pid] for pid in picked])
+
+    def _launch_early(self) -> None:
+        """All gradients of the early bucket are complete (autograd has added them onto the
+        residuals): start their share of the first product on the side stream. Uses descriptor
+        tables bound in an earlier step; nothing is allocated or uploaded here."""
+        native = getattr(self.aggregator._powersgd, "_native", None)
+        if native is not None:
+            native.early_product()
 
     def _fold(self) -> None:
         """p.grad <- residual + fresh gradient for the parameters detached by `_begin`."""
@@ -149,7 +228,7 @@ class TrainStep:
                 fused.fold(self._accumulate, [r for _p, r in live], [p.grad for p, _r in live])
             else:
                 self._accumulate([r for _p, r in live], [p.grad for p, _r in live])
-            self._fold_launches = 1
+            self._fold_launches += 1
         else:
             for p, r in live:
                 r.add_(p.grad)
@@ -176,6 +255,11 @@ class TrainStep:
         fused = getattr(self.aggregator, "_fused", None)
         if fused is not None:
             self.launches_per_step = getattr(fused, "launches", 0) + getattr(self, "_fold_launches", 0)
+        if self._hook_recording:
+            self._hook_recording = False
+            if fused is not None and getattr(self.aggregator._powersgd, "_native", None) is not None:
+                self._choose_bucket()   # may leave the bucket empty: then nothing is launched early
+                self._bucket_decided = True
         return loss.detach()
 
     @property

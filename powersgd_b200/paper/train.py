@@ -167,11 +167,10 @@ def main():
                         apply_momentum(grads, momenta, first_step=not first_step_done)
 
                 with timer("batch.accumulate", epoch_frac, verbosity=2):
-                    for grad, memory, send in zip(grads, memories, send_buffers):
-                        if config["optimizer_memory"]:
-                            torch.add(grad, memory, out=send)
-                        else:
-                            send.copy_(grad)
+                    # multi-tensor launches (one per operation, not one per parameter)
+                    torch._foreach_copy_(send_buffers, grads)
+                    if config["optimizer_memory"]:
+                        torch._foreach_add_(send_buffers, memories)
 
                 with timer("batch.reduce", epoch_frac):
                     # `grads` now receive the aggregate that every worker applies
@@ -189,8 +188,10 @@ def main():
                 first_step_done = True
 
                 with timer("batch.step", epoch_frac, verbosity=2):
-                    for param, grad, lr in zip(task.state, grads, lrs):
-                        param.data.add_(grad, alpha=-lr)
+                    # one multi-tensor launch per distinct learning rate (usually one)
+                    for lr in sorted(set(lrs)):
+                        picked = [k for k, value in enumerate(lrs) if value == lr]
+                        torch._foreach_add_([task.state[k].data for k in picked], [grads[k] for k in picked], alpha=-lr)
 
                 if config["fix_conv_weight_norm"]:
                     with timer("batch.normfix", epoch_frac, verbosity=2):
