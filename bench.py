@@ -212,6 +212,36 @@ def build_reference(device):
     return Step()
 
 
+def measure_aggregate(step, xs, ys, is_reference: bool, max_over_ranks, graph: bool, bursts: int = 20, burst_len: int = 10):
+    """Device time from the end of backward to the end of the parameter update, in steady state.
+
+    Bursts of steps are enqueued back to back (no host synchronisation inside a burst, so the
+    ranks' GPUs stay coupled as they are in training); the event pair of the LAST step of every
+    burst is read after the burst. Mean over bursts, max over ranks. Returns (ms, description)."""
+    import torch
+
+    if is_reference:
+        step.time_aggregate = True
+    samples = []
+    k = 0
+    for _ in range(bursts):
+        for _ in range(burst_len):
+            step(xs[k % len(xs)], ys[k % len(ys)])
+            k += 1
+        torch.cuda.synchronize()
+        ms = step.aggregate_ms
+        if ms is not None:
+            samples.append(ms)
+    if not samples:
+        return None, "not measured"
+    how = (
+        f"device time from the end of backward to the end of the parameter update: last step of each of {len(samples)} "
+        f"bursts of {burst_len} back-to-back steps after the timed regions, mean, max over ranks; "
+        + ("event-record nodes inside the replayed CUDA graph" if graph else "CUDA-event pair around the aggregation + optimizer call")
+    )
+    return max_over_ranks(sum(samples) / len(samples)), how
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -310,23 +340,8 @@ def main():
     clocks = sampler.stop()
 
     # ---- compress + reduce + update time per step, steady state (outside both timed regions) ----
-    # Bursts of steps enqueued back to back (no host synchronisation inside a burst, so the ranks'
-    # GPUs stay coupled as they are in training); the event pair of the LAST step of every burst
-    # is read after the burst.
-    bursts, burst_len = 20, 10
-    if args.impl == "reference":
-        step.time_aggregate = True
-    agg_samples = []
-    k = 0
-    for _ in range(bursts):
-        for _ in range(burst_len):
-            step(xs_dev[k % n_slots], ys_dev[k % n_slots])
-            k += 1
-        torch.cuda.synchronize()
-        ms = step.aggregate_ms
-        if ms is not None:
-            agg_samples.append(ms)
-    agg_ms = max_over_ranks(sum(agg_samples) / len(agg_samples)) if agg_samples else None
+    agg_ms, agg_how = measure_aggregate(step, xs_dev, ys_dev, args.impl == "reference", max_over_ranks,
+                                        graph=args.impl == "ours" and not args.no_graph)
     barrier()
 
     images = BATCH_PER_GPU * world * args.steps
@@ -371,12 +386,7 @@ def main():
             },
             "gpu_launches": launches,
             "aggregate_ms_per_step": agg_ms,
-            "aggregate_how": (
-                f"device time from the end of backward to the end of the parameter update: last step of each of "
-                f"{len(agg_samples)} bursts of {burst_len} back-to-back steps after the timed regions, mean, max over ranks; "
-                + ("event-record nodes inside the replayed CUDA graph" if args.impl == "ours" and not args.no_graph
-                   else "CUDA-event pair around the aggregation + optimizer call")
-            ),
+            "aggregate_how": agg_how,
         }
         print(json.dumps(out))
     if world > 1:

@@ -46,6 +46,13 @@ def parse():
     ap.add_argument("--skip-reference", action="store_true")
     ap.add_argument("--only-ours", action="store_true", help="time only the native path (used for profiler captures)")
     ap.add_argument("--stages", action="store_true", help="add per-phase device times of the native path to every row")
+    ap.add_argument("--model", choices=["resnet18", "lstm"], default=None,
+                    help="instead of --shapes: the compressed gradient matrices of this model (ResNet-18 with the CIFAR "
+                         "stem: 21 matrices in 12 shape groups; LSTM language model: 33278x650 and 6 x 2600x650), "
+                         "per-phase device times with the product kernels on CUDA cores and on tensor cores")
+    ap.add_argument("--read-floor", action="store_true",
+                    help="add to every row the time of a plain read-only streaming pass over the same gradients "
+                         "(the floor of any kernel that reads them once), cold, CUDA events")
     ap.add_argument("--flat-stages", action="store_true",
                     help="multi-GPU: per-stage device times of the uncompressed peer-store all-reduce (pack, "
                          "scatter + reduce, unpack) next to the library all-reduce, then exit")
@@ -171,6 +178,77 @@ def flat_stages(args, world, rank, device):
         torch.cuda.empty_cache()
 
 
+def read_floor_ms(grads, flush, steps, device) -> float:
+    """Best-of-`steps` device time of one read-only streaming pass over all gradient tensors (one
+    launch each, back to back, between one CUDA-event pair), caches flushed before every sample."""
+    import ctypes
+
+    from powersgd_b200.ops import native
+
+    lib = native.lib()
+    sink = torch.zeros(1, device=device)
+    scratch = flush if flush is not None else torch.zeros(2 * L2_BYTES // 4, device=device)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    best = float("inf")
+    for _ in range(max(steps, 3)):
+        scratch.add_(1.0)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for g in grads:
+            native.check(lib.psgd_read_pass_launch(ctypes.c_void_p(g.data_ptr()), ctypes.c_longlong(g.numel()), ctypes.c_void_p(sink.data_ptr()),
+                                                   148 * 8, stream), "psgd_read_pass_launch")
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b))
+    return best
+
+
+def model_table(args, world, rank, device):
+    """Per-phase device times of one aggregate() on the gradient shapes of a whole model, once with
+    the CUDA-core product kernels and once with the tensor-core ones wherever TMA can address the
+    matrix (CUDA-event pairs between the launches, L2 flushed between iterations, max over ranks)."""
+    from powersgd_b200 import BasicConfig, BasicPowerSGD, Config
+    from powersgd_b200.plan import should_compress
+
+    if args.model == "resnet18":
+        from powersgd_b200.models import ResNet18
+
+        net, r, iters = ResNet18(), 2, 2
+    else:
+        from powersgd_b200.models import wikitext2_lstm
+
+        net, r, iters = wikitext2_lstm(33278), 4, 1
+    cfg = Config(rank=r, min_compression_rate=2, num_iters_per_step=iters, start_compressing_after_num_steps=0)
+    seen, shapes = set(), []
+    for p in net.parameters():
+        if id(p) in seen:
+            continue  # tied weights
+        seen.add(id(p))
+        if should_compress(p.shape, cfg):
+            shapes.append(tuple(p.shape))
+    g = torch.Generator(device="cpu").manual_seed(3 + rank)
+    grads = []
+    for s_ in shapes:
+        n = s_[0]
+        m = int(torch.Size(s_).numel() // n)
+        a = torch.randn(n, 8, generator=g).to(device) @ torch.randn(8, m, generator=g).to(device)
+        a.add_(torch.randn(n, m, generator=g).to(device), alpha=1e-3 ** 0.5)
+        grads.append(a.view(s_))
+    nbytes = 4 * sum(t.numel() for t in grads)
+    flush = torch.zeros(2 * L2_BYTES // 4, device=device)
+    for mode in ("ffma", "tc"):
+        os.environ["PSGD_B200_GEMM"] = mode
+        stages = {}
+        ms, err, _ = time_aggregate(lambda: BasicPowerSGD(grads, BasicConfig(rank=r, num_iters_per_step=iters), backend="native"),
+                                    grads, args.steps, args.warmup, flush, world, device, stages=stages)
+        if rank == 0:
+            print(json.dumps({"model": args.model, "matrices": len(grads), "mbytes": nbytes / 1e6, "rank": r, "iters": iters,
+                              "n_gpus": world, "products": mode, "ours_ms": ms, "ours_phase_ms": stages,
+                              "l2": "flush between iterations"}), flush=True)
+    os.environ.pop("PSGD_B200_GEMM", None)
+
+
 def main():
     args = parse()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -188,6 +266,12 @@ def main():
             raise SystemExit("--flat-stages needs at least two ranks")
         flat_stages(args, world, rank, device)
         dist.destroy_process_group()
+        return
+
+    if args.model:
+        model_table(args, world, rank, device)
+        if world > 1:
+            dist.destroy_process_group()
         return
 
     ref = None if (args.skip_reference or args.only_ours) else reference_module()
@@ -220,6 +304,9 @@ def main():
                 }
                 if stages:
                     row["ours_phase_ms"] = stages
+                if args.read_floor:
+                    row["read_pass_ms"] = read_floor_ms(grads, flush, args.steps, device)
+                    row["read_pass_gbs"] = nbytes / (row["read_pass_ms"] * 1e-3) / 1e9
                 # algorithmic traffic: `iters` reads of M, then read M + write residual + write update
                 traffic = (iters + 3) * nbytes
                 row["ours_gbs"] = traffic / (ours_ms * 1e-3) / 1e9

@@ -115,14 +115,29 @@ def build(model_name: str, impl: str, device, use_graph: bool):
 
         class Step:
             launches_per_step = 0
-            aggregate_ms = None
+            time_aggregate = False   # switched on for the separate aggregate-timing pass only
+            _pair = None
+
+            @property
+            def aggregate_ms(self):
+                if self._pair is None:
+                    return None
+                a, b = self._pair
+                b.synchronize()
+                return a.elapsed_time(b)
 
             def __call__(self, x, y):
                 loss = flat_ce(model(x), y)
                 loss.backward()
+                if self.time_aggregate:
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
                 if clip is not None:
                     torch.nn.utils.clip_grad_norm_(params, clip)
                 ref.optimizer_step(optimizer, agg)
+                if self.time_aggregate:
+                    b.record()
+                    self._pair = (a, b)
                 return loss.detach()
 
         step = Step()
@@ -190,6 +205,9 @@ def main():
     barrier()
     e2e_ms = max_over_ranks(c.elapsed_time(d))
     clocks = sampler.stop()
+    agg_ms, agg_how = headline.measure_aggregate(step, xs_dev, ys_dev, args.impl == "reference", max_over_ranks,
+                                                 graph=args.impl == "ours" and not args.no_graph, bursts=8, burst_len=5)
+    barrier()
     tokens = tokens_per_step * world * args.steps
     if rank == 0:
         print(json.dumps({
@@ -199,13 +217,15 @@ def main():
             "dtype": "fp32" if args.model == "lstm" else "bf16 autocast, fp32 parameters and gradients",
             "data": "synthetic Zipf(s=1) tokens, random-init weights",
             "config": {"model": args.model, "tokens_per_step_per_gpu": tokens_per_step, "parallelism": f"dp{world}",
-                       "powersgd": cfg, "optimizer": opt_kw, "cuda_graph": bool(args.impl == "ours" and not args.no_graph),
+                       "powersgd": cfg, "optimizer": opt_kw,
                        "l2": "per-step working set exceeds L2; no explicit flush"},
+            "engine": {"cuda_graph": bool(args.impl == "ours" and not args.no_graph), "host_cpus": os.cpu_count()},
             "clocks": clocks,
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": 2 * 8 * tokens_per_step, "d2h_bytes_per_step": 4, "last_loss": last},
             "gpu_launches": getattr(step, "launches_per_step", 0) * args.steps,
-            "aggregate_ms_per_step": getattr(step, "aggregate_ms", None),
+            "aggregate_ms_per_step": agg_ms,
+            "aggregate_how": agg_how,
         }))
     if world > 1:
         dist.destroy_process_group()

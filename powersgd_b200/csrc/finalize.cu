@@ -12,6 +12,7 @@
 //     or        SGD with momentum / dampening / nesterov / weight decay applied to `param`
 // HBM traffic: read + write M, plus param / momentum when fused. The rank-(T*r) updates run on
 // FP32 FMAs from shared-memory panels (4x4 register micro-tiles).
+#include "psgd_bounds.cuh"
 #include "psgd_comm.cuh"
 
 constexpr int FIN_THREADS = 256;
@@ -269,6 +270,19 @@ __device__ __forceinline__ void finalize_strip_tile(const FinalizeArgs& a, const
   float* sRs = SAME ? sRl : sLl + K * tile_rows;
   float* sLs = SAME ? sLl : sRs + K * FIN_COLS;
 
+#ifdef PSGD_BOUNDS_CHECK
+  {
+    bool ok = true;
+    ok &= PSGD_BC(t.row0 >= 0 && t.rows > 0 && t.row0 + t.rows <= mt.n && t.rows <= tile_rows, 3, PSGD_BC_TILE_ROWS, t.row0 + t.rows, mt.n);
+    ok &= PSGD_BC(t.col0 >= 0 && t.cols > 0 && t.col0 + t.cols <= mt.m && t.cols <= FIN_COLS, 3, PSGD_BC_TILE_COLS, t.col0 + t.cols, mt.m);
+    ok &= PSGD_BC(K >= 1 && K <= FIN_STRIP_KMAX && (SAME ? 1 : 2) * K * (FIN_COLS + tile_rows) * 4 <= 48 * 1024, 3, PSGD_BC_SMEM, K, FIN_STRIP_KMAX);
+    const unsigned long long addr = (unsigned long long)mt.grad | (unsigned long long)mt.param | (unsigned long long)mt.mom | (unsigned long long)mt.out;
+    ok &= PSGD_BC(t.vec == 1 || (t.vec == 2 && addr % 8 == 0 && mt.m % 2 == 0) || (t.vec == 4 && addr % 16 == 0 && mt.m % 4 == 0),
+                  3, PSGD_BC_ALIGNMENT, addr % 16, t.vec);
+    ok &= PSGD_BC(!a.fused_sgd || mt.param != nullptr, 3, PSGD_BC_ELEMENT, 0, 0);
+    if (!ok) return;
+  }
+#endif
   const bool gather = !SAME && a.comm != nullptr;
   int e1 = 0;
   bool ok = true;
@@ -542,6 +556,9 @@ __device__ __forceinline__ void flat_wait_gathered(const FlatArgs& a, const Psgd
 __global__ void __launch_bounds__(FLAT_THREADS) psgd_flat_kernel(FlatArgs a) {
   const PsgdFlat it = a.items[a.block_item[blockIdx.x]];
   const long long first = a.block_first[blockIdx.x];
+#ifdef PSGD_BOUNDS_CHECK
+  if (!PSGD_BC(first >= 0 && first < it.numel, 4, PSGD_BC_ELEMENT, first, it.numel)) return;
+#endif
   const PsgdHyper h = a.hyper[it.hyper];
   PsgdCommDev c;
   int e1 = 0;
@@ -765,3 +782,7 @@ PSGD_API int psgd_flat_launch(int mode, int vec, const void* items, const int* b
   PSGD_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+#ifdef PSGD_BOUNDS_CHECK
+PSGD_BOUNDS_EXPORT(psgd_bounds_read_finalize)
+#endif

@@ -18,12 +18,13 @@
 // Tiles that cover the same output rows (NT: row blocks of one column block; NN: column
 // blocks of one row block) write partial sums to a scratch arena; the tile that arrives last
 // (arrival counter) adds them in a fixed order, so the result does not depend on scheduling.
+#include "psgd_bounds.cuh"
 #include "psgd_comm.cuh"
 
 constexpr int GEMM_THREADS = 256;
 constexpr int GEMM_WARPS = GEMM_THREADS / 32;
 constexpr int NT_TILE_COLS = 128;   // columns of M per NT tile
-constexpr int NT_MAX_ROWS = 256;    // rows of M per NT tile (P-hat block staged in smem); 128 at RT = 32
+constexpr int NT_MAX_ROWS = 256;    // rows of P-hat staged in smem at a time (128 at RT = 32); a tile may span several such chunks
 constexpr int NN_CHUNK_COLS = 128;  // columns consumed per inner iteration of an NN tile
 
 struct GemmArgs {
@@ -41,6 +42,35 @@ struct GemmArgs {
   // epoch, into slot[rank] of every peer's arena. Null for a single worker.
   const PsgdCommDev* comm;
 };
+
+#ifdef PSGD_BOUNDS_CHECK
+// Capacities of the buffers behind the raw pointers (floats / counters), set by the host through
+// psgd_debug_limits_products() before a checked run; 0 = unknown, not checked.
+static __device__ long long g_lim_partial, g_lim_tickets, g_lim_p, g_lim_q;
+
+// Validates one product tile against its matrix, the template rank, the access width it claims and
+// the scratch capacities. All threads compute the same verdict; a CTA with a bad tile returns
+// before it touches memory.
+template <int RT>
+__device__ __forceinline__ bool product_tile_ok(const PsgdTile& t, const PsgdMat& mt, int kernel_id, int max_rows,
+                                                int max_cols, int tile_elems) {
+  bool ok = true;
+  ok &= PSGD_BC(t.row0 >= 0 && t.rows > 0 && t.row0 + t.rows <= mt.n && t.rows <= max_rows, kernel_id, PSGD_BC_TILE_ROWS, t.row0 + t.rows, mt.n);
+  ok &= PSGD_BC(t.col0 >= 0 && t.cols > 0 && t.col0 + t.cols <= mt.m && t.cols <= max_cols, kernel_id, PSGD_BC_TILE_COLS, t.col0 + t.cols, mt.m);
+  ok &= PSGD_BC(mt.r >= 1 && mt.r <= RT, kernel_id, PSGD_BC_RANK, mt.r, RT);
+  const unsigned long long addr = (unsigned long long)mt.grad;
+  ok &= PSGD_BC(t.vec == 1 || (t.vec == 2 && addr % 8 == 0 && mt.m % 2 == 0) || (t.vec == 4 && addr % 16 == 0 && mt.m % 4 == 0),
+                kernel_id, PSGD_BC_ALIGNMENT, addr % 16, t.vec);
+  ok &= PSGD_BC(t.nsplit >= 1 && t.split >= 0 && t.split < t.nsplit, kernel_id, PSGD_BC_SCRATCH_SLOT, t.split, t.nsplit);
+  if (t.nsplit > 1 && g_lim_partial > 0)
+    ok &= PSGD_BC((long long)(t.slot0 + t.nsplit) * tile_elems <= g_lim_partial, kernel_id, PSGD_BC_SCRATCH_SLOT,
+                  (long long)(t.slot0 + t.nsplit) * tile_elems, g_lim_partial);
+  if (t.nsplit > 1 && g_lim_tickets > 0) ok &= PSGD_BC(t.ticket >= 0 && t.ticket < g_lim_tickets, kernel_id, PSGD_BC_TICKET, t.ticket, g_lim_tickets);
+  if (g_lim_p > 0) ok &= PSGD_BC((long long)mt.p_off + (long long)mt.n * mt.r <= g_lim_p, kernel_id, PSGD_BC_FACTOR_INDEX, (long long)mt.p_off + (long long)mt.n * mt.r, g_lim_p);
+  if (g_lim_q > 0) ok &= PSGD_BC((long long)mt.q_off + (long long)mt.m * mt.r <= g_lim_q, kernel_id, PSGD_BC_FACTOR_INDEX, (long long)mt.q_off + (long long)mt.m * mt.r, g_lim_q);
+  return ok;
+}
+#endif
 
 template <int RT>
 __host__ __device__ constexpr int nt_max_rows() { return RT <= 16 ? NT_MAX_ROWS : NT_MAX_ROWS / 2; }
@@ -75,6 +105,24 @@ __device__ __forceinline__ void load_lane_cols(const float* __restrict__ rowp, i
   }
 }
 
+// Sum of element `e` over the `n` partial tiles of one output block, in split order (fixed, so the
+// result does not depend on which tile arrived last). Eight loads are in flight at a time: a tall
+// matrix has a hundred partial tiles per block, and one dependent L2 round trip per partial would
+// cost the last arriver tens of microseconds.
+__device__ __forceinline__ float sum_partials(const float* first, int tile_elems, int n) {
+  float s = 0.f;
+  int p = 0;
+  for (; p + 8 <= n; p += 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __ldcg(first + (long long)(p + j) * tile_elems);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += v[j];
+  }
+  for (; p < n; ++p) s += __ldcg(first + (long long)p * tile_elems);
+  return s;
+}
+
 // ------------------------------------------------------------------------------------------
 // NT: each lane owns 4 columns, each warp strides over the tile's rows.
 // ------------------------------------------------------------------------------------------
@@ -86,14 +134,9 @@ __device__ __forceinline__ void gemm_nt_tile(const GemmArgs& a, const PsgdTile& 
   float* sP = smem;                        // [rows][RT]
   float* sSum = smem + nt_max_rows<RT>() * RT;   // [128][RT]
   __shared__ int sLast;
-
-  // stage the tile's rows of P-hat (zero padded to RT columns)
-  const float* __restrict__ pin = a.in + mt.p_off + (long long)t.row0 * r;
-  for (int e = tid; e < t.rows * RT; e += GEMM_THREADS) {
-    const int row = e / RT, k = e % RT;
-    sP[e] = (k < r) ? pin[row * r + k] : 0.f;
-  }
-  __syncthreads();
+#ifdef PSGD_BOUNDS_CHECK
+  if (!product_tile_ok<RT>(t, mt, 1, 1 << 30, NT_TILE_COLS, NT_TILE_COLS * RT)) return;
+#endif
 
   float acc[4][RT];
 #pragma unroll
@@ -103,29 +146,46 @@ __device__ __forceinline__ void gemm_nt_tile(const GemmArgs& a, const PsgdTile& 
 
   const float* __restrict__ M = mt.grad;
   const int cend = t.col0 + t.cols;
+  constexpr int MAXR = nt_max_rows<RT>();
 
-  for (int i0 = warp; i0 < t.rows; i0 += GEMM_WARPS * 4) {
-    float v[4][4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int i = i0 + u * GEMM_WARPS;
-      const bool rok = i < t.rows;
-      load_lane_cols<VEC>(M + (long long)(t.row0 + (rok ? i : 0)) * m, t.col0, cend, lane, rok, v[u]);
+  // a tall tile is walked in chunks of MAXR rows (what fits the staging buffer of P-hat); the
+  // accumulators live across chunks, so a matrix with tens of thousands of rows needs tens of
+  // partial tiles per column block, not hundreds
+  for (int rb = 0; rb < t.rows; rb += MAXR) {
+    const int rows = min(MAXR, t.rows - rb);
+    if (rb) __syncthreads();  // the previous chunk's rows of P-hat are no longer read
+    // stage the chunk's rows of P-hat (zero padded to RT columns)
+    const float* __restrict__ pin = a.in + mt.p_off + (long long)(t.row0 + rb) * r;
+    for (int e = tid; e < rows * RT; e += GEMM_THREADS) {
+      const int row = e / RT, k = e % RT;
+      sP[e] = (k < r) ? pin[row * r + k] : 0.f;
     }
+    __syncthreads();
+
+    for (int i0 = warp; i0 < rows; i0 += GEMM_WARPS * 4) {
+      float v[4][4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int i = i0 + u * GEMM_WARPS;
-      if (i < t.rows) {
-        const float* pr = sP + i * RT;
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * GEMM_WARPS;
+        const bool rok = i < rows;
+        load_lane_cols<VEC>(M + (long long)(t.row0 + rb + (rok ? i : 0)) * m, t.col0, cend, lane, rok, v[u]);
+      }
 #pragma unroll
-        for (int k = 0; k < RT; ++k) {
-          const float pk = pr[k];
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * GEMM_WARPS;
+        if (i < rows) {
+          const float* pr = sP + i * RT;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) acc[c][k] = fmaf(v[u][c], pk, acc[c][k]);
+          for (int k = 0; k < RT; ++k) {
+            const float pk = pr[k];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[c][k] = fmaf(v[u][c], pk, acc[c][k]);
+          }
         }
       }
     }
   }
+  __syncthreads();
 
   // deterministic cross-warp sum: warps add in index order
   for (int w = 0; w < GEMM_WARPS; ++w) {
@@ -155,11 +215,7 @@ __device__ __forceinline__ void gemm_nt_tile(const GemmArgs& a, const PsgdTile& 
     owner = sLast != 0;
     if (owner) {
       __threadfence();
-      for (int e = tid; e < tile_elems; e += GEMM_THREADS) {
-        float s = 0.f;
-        for (int p = 0; p < t.nsplit; ++p) s += __ldcg(a.partial + (long long)(t.slot0 + p) * tile_elems + e);
-        sSum[e] = s;
-      }
+      for (int e = tid; e < tile_elems; e += GEMM_THREADS) sSum[e] = sum_partials(a.partial + (long long)t.slot0 * tile_elems + e, tile_elems, t.nsplit);
       if (tid == 0) a.tickets[t.ticket] = 0;  // ready for the next launch
       __syncthreads();
     }
@@ -212,6 +268,9 @@ __device__ __forceinline__ void gemm_nn_tile(const GemmArgs& a, const PsgdTile& 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int TILE_ROWS = GEMM_WARPS * RPW;
   __shared__ int sLast;
+#ifdef PSGD_BOUNDS_CHECK
+  if (!product_tile_ok<RT>(t, mt, 2, TILE_ROWS, 1 << 30, TILE_ROWS * RT)) return;
+#endif
 
   const float* __restrict__ M = mt.grad;
   const float* __restrict__ qin = a.in + mt.q_off;
@@ -272,11 +331,7 @@ __device__ __forceinline__ void gemm_nn_tile(const GemmArgs& a, const PsgdTile& 
     owner = sLast != 0;
     if (owner) {
       __threadfence();
-      for (int e = tid; e < tile_elems; e += GEMM_THREADS) {
-        float s = 0.f;
-        for (int p = 0; p < t.nsplit; ++p) s += __ldcg(a.partial + (long long)(t.slot0 + p) * tile_elems + e);
-        sSum[e] = s;
-      }
+      for (int e = tid; e < tile_elems; e += GEMM_THREADS) sSum[e] = sum_partials(a.partial + (long long)t.slot0 * tile_elems + e, tile_elems, t.nsplit);
       if (tid == 0) a.tickets[t.ticket] = 0;
       __syncthreads();
     }
@@ -396,3 +451,16 @@ PSGD_API int psgd_gemm_ffma_launch(int transposed, int max_r, const void* mats, 
   if (transposed) { PSGD_DISPATCH_RT(launch_nt) }
   PSGD_DISPATCH_RT(launch_nn)
 }
+
+#ifdef PSGD_BOUNDS_CHECK
+PSGD_BOUNDS_EXPORT(psgd_bounds_read_products)
+// Capacities (floats / counters) of the partial-sum arena, the ticket table and the P- and Q-shaped
+// factor buffers of the launches that follow; 0 leaves a capacity unchecked.
+PSGD_API int psgd_debug_limits_products(long long partial_floats, long long tickets, long long p_floats, long long q_floats) {
+  PSGD_CUDA_OK(cudaMemcpyToSymbol(g_lim_partial, &partial_floats, sizeof(long long)));
+  PSGD_CUDA_OK(cudaMemcpyToSymbol(g_lim_tickets, &tickets, sizeof(long long)));
+  PSGD_CUDA_OK(cudaMemcpyToSymbol(g_lim_p, &p_floats, sizeof(long long)));
+  PSGD_CUDA_OK(cudaMemcpyToSymbol(g_lim_q, &q_floats, sizeof(long long)));
+  return 0;
+}
+#endif

@@ -31,6 +31,7 @@
 // in-kernel all-reduce (powersgd/powersgd.py:205-209 in the reference is a blocking library
 // call): while staging its chunk every CTA polls the tagged words of the W slots, adds them in
 // rank order, and writes the sum to the factor buffer and to the copy the decompression reads.
+#include "psgd_bounds.cuh"
 #include "psgd_comm.cuh"
 
 typedef struct {
@@ -117,6 +118,16 @@ __global__ void __launch_bounds__(ORTH_THREADS) psgd_orth_gram_kernel(OrthArgs a
   const int r = u.r;
   const int tid = threadIdx.x;
   const float* __restrict__ x = a.x + u.x_off;
+#ifdef PSGD_BOUNDS_CHECK
+  {
+    bool ok = true;
+    ok &= PSGD_BC(r >= 1 && r <= RT, 5, PSGD_BC_RANK, r, RT);
+    ok &= PSGD_BC(ch.row0 >= 0 && ch.rows > 0 && (long long)ch.row0 + ch.rows <= (long long)u.sub_len * u.nsub && ch.rows * RT <= ORTH_CHUNK_FLOATS,
+                  5, PSGD_BC_CHUNK, (long long)ch.row0 + ch.rows, (long long)u.sub_len * u.nsub);
+    ok &= PSGD_BC((int)blockIdx.x >= u.chunk0 && (int)blockIdx.x < u.chunk0 + u.nchunks, 5, PSGD_BC_CHUNK, blockIdx.x, u.chunk0 + u.nchunks);
+    if (!ok) return;
+  }
+#endif
 
   __shared__ __align__(16) double sx[ORTH_CHUNK_FLOATS];
   __shared__ __align__(16) double sf[ORTH_CHUNK_FLOATS];
@@ -442,3 +453,7 @@ PSGD_API int psgd_orth_launch(const void* units, int nunits, const void* chunks,
   PSGD_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+#ifdef PSGD_BOUNDS_CHECK
+PSGD_BOUNDS_EXPORT(psgd_bounds_read_orth)
+#endif

@@ -33,3 +33,20 @@ PSGD_API int psgd_device_info(int* sm_count, int* cc_major, int* cc_minor, int* 
   *max_smem_optin = (int)prop.sharedMemPerBlockOptin;
   return 0;
 }
+
+#ifdef PSGD_BOUNDS_CHECK
+extern "C" int psgd_bounds_read_products(int* out, int reset);
+extern "C" int psgd_bounds_read_finalize(int* out, int reset);
+extern "C" int psgd_bounds_read_orth(int* out, int reset);
+// Debug build only. out[0..23]: the status blocks of the product, decompression / flat and
+// orthonormalisation translation units (8 ints each: violations, kernel id of the first, what,
+// value lo / hi, limit lo / hi, unused). Returns the total number of violations, or -1 on error.
+PSGD_API int psgd_bounds_status(int* out, int reset) {
+  if (psgd_bounds_read_products(out, reset) != 0 || psgd_bounds_read_finalize(out + 8, reset) != 0 ||
+      psgd_bounds_read_orth(out + 16, reset) != 0) {
+    psgd_set_error("psgd_bounds_status: reading a status block failed");
+    return -1;
+  }
+  return out[0] + out[8] + out[16];
+}
+#endif

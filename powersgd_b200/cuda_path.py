@@ -191,7 +191,11 @@ class TilePlan:
                     ticket += 1
                     tc_slots += len(col_blocks)
                 continue
-            row_blocks = _split_even(g.n, self.nt_rows, 1)
+            # tall matrices: tiles of 256 rows (128 KiB: small enough that every SM holds several at
+            # any time, which is what hides the load latency) but never more than 160 partial tiles
+            # per column block (the kernel walks a taller tile in chunks of its staging buffer)
+            rows_per_tile = max(self.nt_rows if g.n <= 4096 else 256, -(-(-(-g.n // 160)) // 128) * 128)
+            row_blocks = _split_even(g.n, rows_per_tile, 1)
             for c0 in range(0, g.m, 128):
                 cols = min(128, g.m - c0)
                 for si, (r0, rows) in enumerate(row_blocks):
@@ -431,6 +435,9 @@ class NativeCompressor:
         self._maps_dev = _to_device(maps, self.device)
         self._tc_split = os.environ.get("PSGD_B200_TC_PRECISION", "split") != "tf32"
         self.uses_tensor_cores = any(tc)
+        # compressed-list positions whose products run on the tensor-core kernels (one launch per
+        # half-iteration for all of them; they are not split into an early and a late bucket)
+        self.tensor_core_positions = frozenset(idx for (_gi, _pos, idx), flag in zip(self.tiles.mats, tc) if flag)
         tile_arrays = self.tiles.build(vec, tc)
         self._tile_arrays = tile_arrays
         self._tiles_dev: Dict[str, Dict[int, Tuple[torch.Tensor, int]]] = {}

@@ -192,8 +192,9 @@ class TrainStep:
         position = {id(p): i for i, p in enumerate(compressed)}
         total = sum(p.numel() for p in compressed)
         picked, acc = [], 0
+        on_tensor_cores = getattr(native, "tensor_core_positions", frozenset())
         for pid in self._hook_order:
-            if pid not in position or acc >= 0.6 * total:
+            if pid not in position or acc >= 0.6 * total or position[pid] in on_tensor_cores:
                 continue
             picked.append(pid)
             acc += by_id[pid].numel()

@@ -64,6 +64,8 @@ _OPTIONAL = {
     "psgd_bulk_arena_bytes": (i64, [i64, i32]),
     "psgd_bulk_allreduce_launch": (i32, [vp, i64, i32, vp]),
     "psgd_bulk_finish_launch": (i32, [vp, i64, i32, vp]),
+    "psgd_read_pass_launch": (i32, [vp, i64, vp, i32, vp]),
+    "psgd_finalize_uses_strip": (i32, [i32, i32, i32, i32]),
     "psgd_symm_alloc": (i32, [C.c_size_t, C.POINTER(vp)]),
     "psgd_symm_free": (i32, [vp]),
     "psgd_symm_handle_bytes": (i32, []),
