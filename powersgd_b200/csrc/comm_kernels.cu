@@ -63,6 +63,41 @@ PSGD_API int psgd_allreduce_oneshot_launch(const void* comm, const float* in, fl
   return 0;
 }
 
+// All-gather of `n` 32-bit words per rank in a single launch: every thread pushes its words (tagged)
+// into slot[rank] of every peer, then polls the W slots of the own arena and writes them out rank
+// after rank. Replaces the library all_gather of the sign, top-k and SVD reducers
+// (paper-code/gradient_reducers.py:69-70, 133, 180, 259-260, 330-331, 631-633). Words are moved as
+// bit patterns, so any 4-byte element type (packed sign words, int32 positions, float values) works.
+__global__ void __launch_bounds__(RED_THREADS) psgd_allgather_oneshot_kernel(const PsgdCommDev* comm,
+                                                                               const uint32_t* __restrict__ in,
+                                                                               uint32_t* __restrict__ out, long long n) {
+  const PsgdCommDev c = *comm;
+  const int e1 = *c.epoch + 1;
+  const long long stride = (long long)gridDim.x * RED_THREADS;
+  const long long start = (long long)blockIdx.x * RED_THREADS + threadIdx.x;
+  for (long long i = start; i < n; i += stride) {
+    const float v = __uint_as_float(in[i]);
+    for (int p = 0; p < c.world; ++p) psgd_comm_store(psgd_comm_slot(c, p, e1, c.rank) + i, v, e1);
+  }
+  bool ok = true;
+  for (long long i = start; i < n; i += stride)
+    for (int r = 0; r < c.world; ++r)
+      out[(long long)r * n + i] = __float_as_uint(psgd_comm_load(c, psgd_comm_slot(c, c.rank, e1, r) + i, e1, ok));
+  psgd_comm_close_epoch(c, e1);
+}
+
+PSGD_API int psgd_allgather_oneshot_launch(const void* comm, const void* in, void* out, long long n, int max_blocks,
+                                           cudaStream_t stream) {
+  if (n <= 0) return 0;
+  long long blocks = (n + RED_THREADS * 2 - 1) / (RED_THREADS * 2);
+  if (max_blocks <= 0) max_blocks = 296;
+  if (blocks > max_blocks) blocks = max_blocks;
+  psgd_allgather_oneshot_kernel<<<(int)blocks, RED_THREADS, 0, stream>>>((const PsgdCommDev*)comm, (const uint32_t*)in,
+                                                                        (uint32_t*)out, n);
+  PSGD_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 // ---- bulk two-shot all-reduce of the flat data region of the arena --------------------------
 // Step 1 (this kernel): push every chunk of the slices that other ranks own into the owner's
 // landing area, then publish the chunk's flag there. Nothing is loaded across the link.

@@ -78,4 +78,5 @@ _OPTIONAL = {
     "psgd_comm_fill": (i32, [vp, i32, i32, vp, vp, vp, i64, C.c_double]),
     "psgd_factor_reduce_launch": (i32, [vp, i64, vp, vp, vp]),
     "psgd_allreduce_oneshot_launch": (i32, [vp, vp, vp, i64, f32, i32, vp]),
+    "psgd_allgather_oneshot_launch": (i32, [vp, vp, vp, i64, i32, vp]),
 }

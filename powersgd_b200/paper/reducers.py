@@ -23,6 +23,7 @@ Reducers, with the reference lines they restate:
 """
 from __future__ import annotations
 
+import os
 from typing import List, Sequence, Tuple
 
 import numpy as np
@@ -64,8 +65,18 @@ def _wait(handle) -> None:
 
 
 def _gather_all(tensor: torch.Tensor, workers: int) -> List[torch.Tensor]:
+    """Every worker's `tensor` (same shape everywhere). CUDA tensors of 4-byte elements travel
+    through this package's in-kernel all-gather (peer stores, one launch); PSGD_B200_COMM=nccl or
+    anything else goes through the library collective."""
     if workers == 1:
         return [tensor]
+    if tensor.is_cuda and tensor.element_size() == 4 and os.environ.get("PSGD_B200_COMM", "p2p") == "p2p":
+        from ..ops import native
+
+        if native.use_for_cuda():
+            from ..parallel.symm import native_all_gather
+
+            return native_all_gather(tensor)
     outs = [torch.empty_like(tensor) for _ in range(workers)]
     dist.all_gather(outs, tensor)
     return outs

@@ -227,6 +227,22 @@ class Channel:
         )
         return tensor
 
+    def all_gather(self, tensor: torch.Tensor, max_blocks: int = 296) -> torch.Tensor:
+        """One-launch all-gather of a contiguous tensor of 4-byte elements (same length on every
+        rank): returns a [world, numel] tensor of the same dtype, rank r's data in row r."""
+        n = tensor.numel()
+        if tensor.element_size() != 4 or not tensor.is_contiguous():
+            raise ValueError("in-kernel all-gather moves contiguous tensors of 4-byte elements")
+        if n > self.cap:
+            raise ValueError(f"message of {n} words exceeds the channel capacity {self.cap}")
+        out = torch.empty((self.world, n), dtype=tensor.dtype, device=tensor.device)
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        native.check(
+            self.lib.psgd_allgather_oneshot_launch(self.ptr, _vp(tensor.data_ptr()), _vp(out.data_ptr()), ctypes.c_longlong(n), max_blocks, stream),
+            "psgd_allgather_oneshot_launch",
+        )
+        return out
+
     def close(self) -> None:
         self.slots.close()
         self._status.close()
@@ -268,3 +284,30 @@ class BulkAllReduce:
         self.buffer = None
         self.channel.close()
 
+
+
+_gather_channels: dict = {}
+
+
+def native_all_gather(tensor: torch.Tensor, group=None) -> List[torch.Tensor]:
+    """All-gather through the in-kernel collectives: list of per-rank tensors shaped like `tensor`.
+    Collective: every rank calls it with a tensor of the same size. The channel behind it is cached
+    per device and grows (a new, larger one is built by all ranks together) when a message does not fit."""
+    device = tensor.device
+    n = tensor.numel()
+    ch = _gather_channels.get(device)
+    if ch is None or ch.cap < n:
+        if ch is not None:
+            ch.close()
+        ch = Channel(max(n, 1 << 16), group)
+        _gather_channels[device] = ch
+    ch.check()
+    out = ch.all_gather(tensor.contiguous().view(-1))
+    return [out[r].view(tensor.shape) for r in range(ch.world)]
+
+
+def close_gather_channels() -> None:
+    """Release the cached all-gather channels (collective across ranks)."""
+    for ch in list(_gather_channels.values()):
+        ch.close()
+    _gather_channels.clear()

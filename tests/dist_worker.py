@@ -50,6 +50,16 @@ def scenario_channel_allreduce():
         ch.check()
         assert _rel(x, ref) < 1e-6, (n, _rel(x, ref))
         assert _same_on_all_ranks(x, world)
+    # all-gather of 4-byte words (floats and integer bit patterns, NaN payloads included)
+    for it, n in enumerate([1, 33, 4097, 1 << 18]):
+        g = torch.Generator(device="cpu").manual_seed(500 * it + rank)
+        words = torch.randint(-(2 ** 31), 2 ** 31 - 1, (n,), generator=g, dtype=torch.int64).to(torch.int32).to(dev)
+        expect = [torch.empty_like(words) for _ in range(world)]
+        dist.all_gather(expect, words)
+        got = ch.all_gather(words)
+        torch.cuda.synchronize()
+        ch.check()
+        assert got.shape == (world, n) and torch.equal(got, torch.stack(expect)), n
     # back-to-back launches without host synchronisation (epoch / double-buffer logic)
     x = torch.full((5000,), float(rank + 1), device=dev)
     for _ in range(50):
