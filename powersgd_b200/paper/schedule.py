@@ -149,7 +149,133 @@ def system_characterization(workers=(2, 4, 8), backends=("nccl", "gloo"), repeti
                                                         "device": "cuda" if backend == "nccl" else "cpu"}, script="timings")
 
 
-EXPERIMENTS = {f.__name__: f for f in (scaling_controlled, rank_tuning, ef_compressors, lm_rank, warm_start, system_characterization)}
+def _cifar_job(name: str, reducer: str, n_workers: int, lr: float, seed: int, **extra) -> Job:
+    """A 300-epoch ResNet-18 / CIFAR-10 run with the paper's base optimizer settings."""
+    return Job(name, n_workers, {"seed": seed, "distributed_backend": "nccl", "optimizer_scale_lr_with_factor": n_workers,
+                                 "num_epochs": 300, "log_verbosity": 1, **sgd_config(lr, momentum=0.9, weight_decay=0.0001),
+                                 **optimizer_config(reducer), **extra})
+
+
+def _lr_sweep(reducer: str, rates, n_workers: int) -> Iterator[Job]:
+    for lr in rates:
+        yield _cifar_job(f"{reducer}_{n_workers:02d}workers_lr{lr}", reducer, n_workers, lr, seed=42)
+
+
+def sgd_tuning(n_workers: int = 8) -> Iterator[Job]:
+    """Learning rate of the uncompressed baseline (schedule/neurips19/sgd_tuning.py)."""
+    return _lr_sweep("SGD", [0.2, 0.1, 0.05, 0.025], n_workers)
+
+
+def signum_tuning(n_workers: int = 8) -> Iterator[Job]:
+    """(schedule/neurips19/signum_tuning.py)"""
+    return _lr_sweep("Signum", [0.0001, 0.0002, 0.00005, 0.000025], n_workers)
+
+
+def atomo_tuning(n_workers: int = 8) -> Iterator[Job]:
+    """(schedule/neurips19/atomo_tuning.py)"""
+    return _lr_sweep("Atomo (rank 2)", [0.2, 0.1, 0.05, 0.025], n_workers)
+
+
+def xvvt_tuning(n_workers: int = 8) -> Iterator[Job]:
+    """Unbiased rank-1 compression without error feedback (schedule/neurips19/xvvt_tuning.py)."""
+    return _lr_sweep("Unbiased Rank 1", [0.1, 0.05, 0.025, 0.0125, 0.00625], n_workers)
+
+
+def xvvt_rank2_tuning(n_workers: int = 8) -> Iterator[Job]:
+    """(schedule/neurips19/xvvt_rank2_tuning.py)"""
+    return _lr_sweep("Unbiased Rank 2", [0.1, 0.05, 0.025, 0.0125, 0.00625], n_workers)
+
+
+def top_k_tuning(n_workers: int = 8) -> Iterator[Job]:
+    """Top-K with error feedback at the budgets of rank 1 / 4 / 7 (schedule/neurips19/top_k_tuning.py)."""
+    for compression in [244, 72, 32]:
+        for lr in [0.1, 0.05]:
+            yield _cifar_job(f"Top K (EF)_{n_workers:02d}workers_lr{lr}_{compression}x", "Top K (EF)", n_workers, lr, seed=42,
+                             optimizer_reducer_compression=1 / compression)
+
+
+def right_rank(n_workers: int = 8) -> Iterator[Job]:
+    """Full against half power-iteration steps at ranks 1, 2, 4 (schedule/neurips19/right_rank.py)."""
+    for rank in [1, 2, 4]:
+        for name in (f"Half Rank {rank} (EF)", f"Rank {rank} (EF)"):
+            yield _cifar_job(name, name, n_workers, 0.1, seed=1000)
+
+
+QUALITY_VARIANCE_REDUCERS = [
+    "SGD", "Rank 1 (EF)", "Rank 2 (EF)", "Rank 4 (EF)", "Rank 7 (EF)", "Rank 2 w/o reuse (EF)", "HQ Rank 2 w/o reuse (EF)",
+    "Random K (rank 2) (EF)", "Random K (rank 7) (EF)", "Random Block (rank 2) (EF)", "Random Block (rank 7) (EF)",
+    "Sign+Norm (EF)", "Top K (136x) (EF)", "Top K (32x) (EF)", "Top K (rank 2) (EF)", "Top K (rank 7) (EF)", "Signum",
+    "Unbiased Rank 1", "Unbiased Rank 2", "Atomo (rank 2)", "Atomo (rank 1)",
+]
+
+
+def quality_variance(n_workers: int = 8, seeds=(1, 2, 3)) -> Iterator[Job]:
+    """Every compressor of the main results table at its tuned learning rate, three seeds
+    (schedule/neurips19/quality_variance.py). The original list also names compressors whose
+    classes were never published (`HQ Rank 2 w/o reuse`: two extra power iterations, which the
+    rank-k reducer refuses; `Top K (rank N)`: a stratified top-k); those entries are skipped."""
+    tuned = {"Signum": 0.00005, "Unbiased Rank 1": 0.0125, "Unbiased Rank 2": 0.0125}
+    for reducer in QUALITY_VARIANCE_REDUCERS:
+        try:
+            optimizer_config(reducer)
+        except KeyError:
+            continue
+        for seed in seeds:
+            yield _cifar_job(f"{reducer}_{n_workers:02d}workers_seed{seed}", reducer, n_workers, tuned.get(reducer, 0.1), seed)
+
+
+def _lm_job(name: str, reducer: str, n_workers: int, lr: float, momentum: float, seed: int) -> Job:
+    return Job(name, n_workers, {"seed": seed, "distributed_backend": "nccl", "optimizer_scale_lr_with_factor": n_workers,
+                                 "log_verbosity": 1, **language_modeling_base(), **sgd_config(lr, momentum=momentum, weight_decay=0.0),
+                                 **optimizer_config(reducer)})
+
+
+def lm_sgd_tuning(n_workers: int = 8) -> Iterator[Job]:
+    """(schedule/neurips19/lm_sgd_tuning.py)"""
+    for lr in [2.5, 1.25, 0.6]:
+        yield _lm_job(f"SGD_{n_workers:02d}workers_lr{lr}", "SGD", n_workers, lr, 0.0, seed=42)
+
+
+def lm_signum_tuning(n_workers: int = 8) -> Iterator[Job]:
+    """(schedule/neurips19/lm_signum_tuning.py)"""
+    for lr in [0.0001, 0.0002, 0.00005, 1e-5, 1e-6]:
+        yield _lm_job(f"Signum_{n_workers:02d}workers_lr{lr}", "Signum", n_workers, lr, 0.9, seed=42)
+
+
+def lm_quality_variance(n_workers: int = 8, seeds=(1, 2, 3)) -> Iterator[Job]:
+    """(schedule/neurips19/lm_quality_variance.py)"""
+    for reducer in ["SGD", "Rank 1 (EF)", "Rank 2 (EF)", "Rank 4 (EF)", "Signum"]:
+        lr, momentum = (1e-5, 0.9) if reducer == "Signum" else (1.25, 0.0)
+        for seed in seeds:
+            yield _lm_job(f"{reducer}_{n_workers:02d}workers_seed{seed}", reducer, n_workers, lr, momentum, seed)
+
+
+def varying_rank_ours(n_workers: int = 8, seeds=(1, 2)) -> Iterator[Job]:
+    """This code base's rank 4 / 2 / 1 against plain all-reduce (schedule/pytorch/varying_rank_ours.py)."""
+    for seed in seeds:
+        for label, reducer in [("powersgd-rank4", "Rank 4 (EF)"), ("powersgd-rank2", "Rank 2 (EF)"),
+                               ("powersgd-rank1", "Rank 1 (EF)"), ("all-reduce", "SGD")]:
+            yield _cifar_job(f"{n_workers:02d}workers_{label}_seed{seed}", reducer, n_workers, 0.1, seed)
+
+
+def varying_rank_ddp(n_workers: int = 8, seeds=(2,)) -> Iterator[Job]:
+    """The same comparison through PyTorch DDP's built-in communication hooks
+    (schedule/pytorch/varying_rank.py): PowerSGD hook at ranks 4 / 2 / 1, fp16 compression, plain
+    all-reduce. Runs `paper/train_ddp.py`."""
+    for seed in seeds:
+        for label, hook, rank in [("powersgd-rank4", "PowerSGD", 4), ("powersgd-rank2", "PowerSGD", 2),
+                                  ("powersgd-rank1", "PowerSGD", 1), ("fp16", "fp16", None), ("all-reduce", "allreduce", None)]:
+            cfg = {"seed": seed, "distributed_backend": "nccl", "optimizer_scale_lr_with_factor": n_workers, "log_verbosity": 1,
+                   **sgd_config(0.1, momentum=0.9, weight_decay=0.0001), "optimizer_reducer": hook}
+            if rank is not None:
+                cfg["optimizer_reducer_rank"] = rank
+            yield Job(f"{n_workers:02d}workers_{label}_seed{seed}", n_workers, cfg, script="train_ddp")
+
+
+EXPERIMENTS = {f.__name__: f for f in (
+    scaling_controlled, system_characterization, sgd_tuning, signum_tuning, atomo_tuning, xvvt_tuning, xvvt_rank2_tuning,
+    top_k_tuning, rank_tuning, right_rank, warm_start, ef_compressors, quality_variance, lm_sgd_tuning, lm_signum_tuning,
+    lm_rank, lm_quality_variance, varying_rank_ours, varying_rank_ddp)}
 
 _RUNNER = (
     "import json,sys;from powersgd_b200.paper import {mod} as m;"
@@ -189,3 +315,32 @@ def slurm_script(job: Job, output_dir: str, gpus_per_node: int = 8, partition: s
         "  --rdzv-backend=c10d --rdzv-endpoint=$head:29500 --no-python python -c \\",
         f"  '{_RUNNER.format(mod=job.script)}' '{payload}' {output_dir}", "",
     ])
+
+
+def hyperparameter_record(max_rows: int = 12) -> str:
+    """Markdown record of every experiment's jobs and overrides (what the reference keeps as
+    config dumps in paper-code/hyperparameters.md), generated from the definitions above:
+    `python -m powersgd_b200.paper.schedule > powersgd_b200/paper/HYPERPARAMETERS.md`."""
+    from . import train
+
+    lines = [
+        "# Hyper-parameters of the experiment definitions", "",
+        "Generated by `python -m powersgd_b200.paper.schedule` from `powersgd_b200/paper/schedule.py` (the reference keeps the",
+        "same information as config dumps in paper-code/hyperparameters.md). Every job starts from the defaults of",
+        "`paper/train.py::config` and applies the overrides listed here.", "", "## Defaults", "", "| key | value |", "|---|---|",
+    ]
+    lines += [f"| `{k}` | `{v}` |" for k, v in train.config.items()]
+    for name, gen in EXPERIMENTS.items():
+        jobs = list(gen())
+        lines += ["", f"## {name} ({len(jobs)} jobs)", "", " ".join((gen.__doc__ or "").split()), "",
+                  "| job | workers | script | overrides |", "|---|---|---|---|"]
+        for job in jobs[:max_rows]:
+            overrides = ", ".join(f"{k}={v}" for k, v in job.config_overrides.items())
+            lines.append(f"| {job.name} | {job.n_workers} | {job.script} | {overrides} |")
+        if len(jobs) > max_rows:
+            lines.append(f"| ... {len(jobs) - max_rows} more (same pattern) | | | |")
+    return "\n".join(lines) + "\n"
+
+
+if __name__ == "__main__":
+    sys.stdout.write(hyperparameter_record())

@@ -33,6 +33,15 @@ def test_every_experiment_generates_jobs_and_commands(tmp_path):
         assert text.startswith("#!/bin/bash") and "#SBATCH --nodes=" in text
 
 
+def test_hyperparameter_record_is_current():
+    """The committed record is what the definitions generate (regenerate with
+    `python -m powersgd_b200.paper.schedule > powersgd_b200/paper/HYPERPARAMETERS.md`)."""
+    path = os.path.join(os.path.dirname(schedule.__file__), "HYPERPARAMETERS.md")
+    with open(path) as fp:
+        assert fp.read() == schedule.hyperparameter_record()
+    assert len(schedule.EXPERIMENTS) == 19  # 17 scripts under schedule/neurips19 + 2 under schedule/pytorch
+
+
 def test_launch_timings_job_on_two_gloo_ranks(tmp_path):
     job = schedule.Job("timings_gloo_02", 2, {"distributed_backend": "gloo", "device": "cpu", "repetitions": 2,
                                              "message_sizes": [4, 1024, 65536]}, script="timings")
