@@ -275,7 +275,7 @@ __device__ __forceinline__ void finalize_strip_tile(const FinalizeArgs& a, const
     bool ok = true;
     ok &= PSGD_BC(t.row0 >= 0 && t.rows > 0 && t.row0 + t.rows <= mt.n && t.rows <= tile_rows, 3, PSGD_BC_TILE_ROWS, t.row0 + t.rows, mt.n);
     ok &= PSGD_BC(t.col0 >= 0 && t.cols > 0 && t.col0 + t.cols <= mt.m && t.cols <= FIN_COLS, 3, PSGD_BC_TILE_COLS, t.col0 + t.cols, mt.m);
-    ok &= PSGD_BC(K >= 1 && K <= FIN_STRIP_KMAX && (SAME ? 1 : 2) * K * (FIN_COLS + tile_rows) * 4 <= 48 * 1024, 3, PSGD_BC_SMEM, K, FIN_STRIP_KMAX);
+    ok &= PSGD_BC(K >= 1 && K <= FIN_STRIP_KMAX && (SAME ? 1 : 2) * K * (FIN_COLS + tile_rows) * 4 <= 96 * 1024, 3, PSGD_BC_SMEM, K, FIN_STRIP_KMAX);
     const unsigned long long addr = (unsigned long long)mt.grad | (unsigned long long)mt.param | (unsigned long long)mt.mom | (unsigned long long)mt.out;
     ok &= PSGD_BC(t.vec == 1 || (t.vec == 2 && addr % 8 == 0 && mt.m % 2 == 0) || (t.vec == 4 && addr % 16 == 0 && mt.m % 4 == 0),
                   3, PSGD_BC_ALIGNMENT, addr % 16, t.vec);
@@ -298,7 +298,7 @@ __device__ __forceinline__ void finalize_strip_tile(const FinalizeArgs& a, const
         const int lc = e / r, j = e - lc * r;
         const int pos = fin_panel_pos<VEC>(lc);
         sRl[(h * r + j) * FIN_COLS + pos] = gl[e];
-        if (!SAME && !poll) sRs[(h * r + j) * FIN_COLS + pos] = gs[e];
+        if (!SAME && !poll && gs != gl) sRs[(h * r + j) * FIN_COLS + pos] = gs[e];
       }
       if (poll) {
         const bool writer = t.row0 == 0;
@@ -320,7 +320,7 @@ __device__ __forceinline__ void finalize_strip_tile(const FinalizeArgs& a, const
       for (int e = tid; e < t.rows * r; e += FIN_THREADS) {
         const int lr = e / r, j = e - lr * r;
         sLl[(h * r + j) * tile_rows + lr] = gl[e];
-        if (!SAME && !poll) sLs[(h * r + j) * tile_rows + lr] = gs[e];
+        if (!SAME && !poll && gs != gl) sLs[(h * r + j) * tile_rows + lr] = gs[e];
       }
       if (poll) {
         const bool writer = t.col0 == 0;
@@ -366,21 +366,28 @@ __device__ __forceinline__ void finalize_strip_tile(const FinalizeArgs& a, const
     for (int u = 0; u < 4; ++u)
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) accE[u][c4] = accA[u][c4] = 0.f;
+    for (int h = 0; h < a.nhist; ++h) {
+      // the basis side of a half-iteration is the same array for the local and the summed product:
+      // its panel was staged once and is read once
+      const bool one_left = SAME || a.lloc[h] == a.lsum[h];
+      const bool one_right = SAME || a.rloc[h] == a.rsum[h];
 #pragma unroll 4
-    for (int k = 0; k < K; ++k) {
-      const float4 ll = *reinterpret_cast<const float4*>(sLl + k * tile_rows + rc + warp * 4);
-      const float4 rl = *reinterpret_cast<const float4*>(sRl + k * FIN_COLS + lane * 4);
-      const float4 ls = SAME ? ll : *reinterpret_cast<const float4*>(sLs + k * tile_rows + rc + warp * 4);
-      const float4 rs = SAME ? rl : *reinterpret_cast<const float4*>(sRs + k * FIN_COLS + lane * 4);
-      const float lv[4] = {ll.x, ll.y, ll.z, ll.w}, sv[4] = {ls.x, ls.y, ls.z, ls.w};
-      const float rlv[4] = {rl.x, rl.y, rl.z, rl.w}, rsv[4] = {rs.x, rs.y, rs.z, rs.w};
+      for (int j = 0; j < r; ++j) {
+        const int k = h * r + j;
+        const float4 ll = *reinterpret_cast<const float4*>(sLl + k * tile_rows + rc + warp * 4);
+        const float4 rl = *reinterpret_cast<const float4*>(sRl + k * FIN_COLS + lane * 4);
+        const float4 ls = one_left ? ll : *reinterpret_cast<const float4*>(sLs + k * tile_rows + rc + warp * 4);
+        const float4 rs = one_right ? rl : *reinterpret_cast<const float4*>(sRs + k * FIN_COLS + lane * 4);
+        const float lv[4] = {ll.x, ll.y, ll.z, ll.w}, sv[4] = {ls.x, ls.y, ls.z, ls.w};
+        const float rlv[4] = {rl.x, rl.y, rl.z, rl.w}, rsv[4] = {rs.x, rs.y, rs.z, rs.w};
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < 4; ++u)
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-          accE[u][c4] = fmaf(lv[u], rlv[c4], accE[u][c4]);
-          if (!SAME) accA[u][c4] = fmaf(sv[u], rsv[c4], accA[u][c4]);
-        }
+          for (int c4 = 0; c4 < 4; ++c4) {
+            accE[u][c4] = fmaf(lv[u], rlv[c4], accE[u][c4]);
+            if (!SAME) accA[u][c4] = fmaf(sv[u], rsv[c4], accA[u][c4]);
+          }
+      }
     }
     // ---- residual, mean update, optimizer ----
 #pragma unroll
@@ -416,9 +423,23 @@ __global__ void __launch_bounds__(FIN_THREADS, 2) psgd_finalize_strip_kernel(Fin
   else finalize_strip_tile<1, SAME>(a, t, mt, tile_rows, fin_smem);
 }
 
+// Shared-memory budgets of a strip CTA: the default carve-out serves the small ranks (several CTAs
+// stay resident per SM); when the panels of a 256-row strip do not fit it (K = 32, or K >= 16 with
+// separate local and summed factors), the kernel opts in to a budget that still leaves two CTAs
+// per SM. Taller strips matter there: every strip re-stages 128 + rows panel entries per K.
+constexpr int FIN_SMEM_DEFAULT = 48 * 1024;
+constexpr int FIN_SMEM_OPT_IN = 96 * 1024;
+
 template <bool SAME>
 static int finalize_strip_launch(const FinalizeArgs& a, int ntiles, int tile_rows, int kmax, cudaStream_t stream) {
   const size_t smem = (size_t)(SAME ? 1 : 2) * kmax * (FIN_COLS + tile_rows) * sizeof(float);
+  if (smem > (size_t)FIN_SMEM_DEFAULT) {
+    static bool opted_in = false;   // per instantiation
+    if (!opted_in) {
+      PSGD_CUDA_OK(cudaFuncSetAttribute(psgd_finalize_strip_kernel<SAME>, cudaFuncAttributeMaxDynamicSharedMemorySize, FIN_SMEM_OPT_IN));
+      opted_in = true;
+    }
+  }
   psgd_finalize_strip_kernel<SAME><<<ntiles, FIN_THREADS, smem, stream>>>(a, tile_rows);
   return 0;
 }
@@ -426,8 +447,9 @@ static int finalize_strip_launch(const FinalizeArgs& a, int ntiles, int tile_row
 // Tallest strip (multiple of 32 rows, at most 256) whose panels fit the shared-memory budget.
 PSGD_API int psgd_finalize_strip_rows(int kmax, int same) {
   if (kmax > FIN_STRIP_KMAX) return FIN_ROWS;  // general kernel: strips only save tile overhead
-  const int budget = 48 * 1024;                // no opt-in needed, several CTAs per SM stay resident
-  int rows = budget / ((same ? 1 : 2) * kmax * (int)sizeof(float)) - FIN_COLS;
+  const int per_row = (same ? 1 : 2) * kmax * (int)sizeof(float);
+  int rows = FIN_SMEM_DEFAULT / per_row - FIN_COLS;
+  if (rows < 256) rows = FIN_SMEM_OPT_IN / per_row - FIN_COLS;
   rows = rows / FIN_ROWS * FIN_ROWS;
   return rows > 256 ? 256 : (rows < FIN_ROWS ? FIN_ROWS : rows);
 }
@@ -435,7 +457,7 @@ PSGD_API int psgd_finalize_strip_rows(int kmax, int same) {
 static bool finalize_takes_strip(int nhist, int max_r, int tile_rows, bool same) {
   const int kmax = nhist * max_r;
   const size_t strip_smem = (size_t)(same ? 1 : 2) * kmax * (FIN_COLS + tile_rows) * sizeof(float);
-  return kmax <= FIN_STRIP_KMAX && strip_smem <= 48 * 1024;
+  return kmax <= FIN_STRIP_KMAX && strip_smem <= (size_t)FIN_SMEM_OPT_IN;
 }
 
 // Whether psgd_finalize_launch runs the strip kernel for this configuration; only the strip kernel

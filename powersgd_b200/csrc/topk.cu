@@ -123,3 +123,110 @@ PSGD_API int psgd_topk_abs(const float* x, long long n, long long k, int* worksp
   PSGD_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Combine step of the top-k reducers: after the all-gather every worker holds W lists of
+// (value, position) pairs and adds value / W into dense, zeroed outputs
+// (paper-code/gradient_reducers.py:262-271 and 333-339 do it with one index_add_ per worker).
+// One cooperative launch does the zero fill and the W scatter passes. Positions are unique
+// within a worker's list, so a pass is race-free with plain read-modify-writes; a grid barrier
+// separates the passes, which keeps the summation order (worker 0, 1, ...) fixed and the result
+// bit-identical on every replica and in every run, unlike floating-point atomics.
+namespace {
+
+constexpr int SC_THREADS = 256;
+constexpr int SC_MAX_SEGMENTS = 1024;
+
+struct SparseSeg {
+  float* out;        // dense output of this segment
+  long long numel;   // its length
+  long long end;     // end of this segment's pairs inside a worker's list (exclusive)
+};
+
+// Barrier over all CTAs of a cooperative launch on a counter that only grows (barrier b is passed
+// once it reaches b * gridDim.x). Bounded: a CTA that waits longer than ~2 s gives up (all CTAs of a
+// cooperative launch are resident, so this only guards against a broken launch).
+__device__ bool sc_grid_barrier(unsigned* counter, unsigned& target) {
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x == 0) {
+    target += gridDim.x;
+    __threadfence();
+    atomicAdd(counter, 1u);
+    const unsigned long long t0 = psgd_globaltimer_ns();
+    while (*(volatile unsigned*)counter < target) {
+      if (psgd_globaltimer_ns() - t0 > 2000000000ull) { ok = false; break; }
+    }
+    __threadfence();
+  }
+  return __syncthreads_and(ok ? 1 : 0) != 0;
+}
+
+__global__ void __launch_bounds__(SC_THREADS) psgd_sparse_combine_kernel(const float* __restrict__ values,
+                                                                          const int* __restrict__ positions, int workers,
+                                                                          long long per_worker, const SparseSeg* __restrict__ segs,
+                                                                          int nsegs, float divisor, unsigned* barrier, int* status) {
+  __shared__ long long ends[SC_MAX_SEGMENTS];
+  for (int s = threadIdx.x; s < nsegs; s += SC_THREADS) ends[s] = segs[s].end;
+  __syncthreads();
+  const long long tid = (long long)blockIdx.x * SC_THREADS + threadIdx.x;
+  const long long stride = (long long)gridDim.x * SC_THREADS;
+  for (int s = 0; s < nsegs; ++s) {
+    float* out = segs[s].out;
+    const long long n = segs[s].numel;
+    for (long long i = tid; i < n; i += stride) out[i] = 0.f;
+  }
+  // value * (1 / W) rounded, then added: what torch's division by a scalar followed by index_add_
+  // computes on the GPU (no fused multiply-add), so the result matches that sequence bit for bit
+  const float inv = 1.0f / divisor;
+  unsigned target = 0;
+  for (int w = 0; w < workers; ++w) {
+    if (!sc_grid_barrier(barrier, target)) {
+      if (threadIdx.x == 0) atomicExch(status, 1);
+      return;
+    }
+    const float* val = values + (long long)w * per_worker;
+    const int* pos = positions + (long long)w * per_worker;
+    for (long long j = tid; j < per_worker; j += stride) {
+      int lo = 0, hi = nsegs - 1;   // first segment whose end is above j
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (ends[mid] > j) hi = mid; else lo = mid + 1;
+      }
+      const long long p = pos[j];
+      if (p >= 0 && p < segs[lo].numel) segs[lo].out[p] = __fadd_rn(segs[lo].out[p], __fmul_rn(val[j], inv));
+    }
+  }
+}
+
+}  // namespace
+
+PSGD_API int psgd_sparse_combine_max_segments() { return SC_MAX_SEGMENTS; }
+
+// values / positions: [workers][per_worker] as gathered; segs: device array of `nsegs` SparseSeg
+// (segment s covers pairs [segs[s-1].end, segs[s].end) of every worker's list; positions are local
+// to the segment's output); barrier: one zeroed unsigned per launch; status: set to 1 if the grid
+// barrier gave up. Writes out_s = sum over workers (in rank order) of the scattered value / divisor.
+PSGD_API int psgd_sparse_combine_launch(const float* values, const int* positions, int workers, long long per_worker,
+                                        const void* segs, int nsegs, float divisor, unsigned* barrier, int* status,
+                                        cudaStream_t stream) {
+  if (nsegs <= 0 || workers <= 0) return 0;
+  if (nsegs > SC_MAX_SEGMENTS) {
+    psgd_set_error("psgd_sparse_combine_launch: %d segments exceed the maximum %d", nsegs, SC_MAX_SEGMENTS);
+    return -1;
+  }
+  static int blocks_cached = 0;
+  if (!blocks_cached) {
+    int dev = 0, sms = 0, per_sm = 0;
+    PSGD_CUDA_OK(cudaGetDevice(&dev));
+    PSGD_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    PSGD_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, psgd_sparse_combine_kernel, SC_THREADS, 0));
+    blocks_cached = sms * (per_sm > 4 ? 4 : (per_sm < 1 ? 1 : per_sm));
+  }
+  PSGD_CUDA_OK(cudaMemsetAsync(barrier, 0, sizeof(unsigned), stream));
+  const SparseSeg* segs_t = (const SparseSeg*)segs;
+  void* params[] = {(void*)&values, (void*)&positions, (void*)&workers, (void*)&per_worker, (void*)&segs_t,
+                    (void*)&nsegs, (void*)&divisor, (void*)&barrier, (void*)&status};
+  PSGD_CUDA_OK(cudaLaunchCooperativeKernel((const void*)psgd_sparse_combine_kernel, dim3(blocks_cached), dim3(SC_THREADS), params, 0, stream));
+  return 0;
+}

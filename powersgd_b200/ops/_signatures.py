@@ -58,6 +58,8 @@ _OPTIONAL = {
     "psgd_finalize_tc_launch": (i32, [vp, vp, i32, vp, vp, i32, i32, vp, vp, vp, vp, f32, i32, vp, vp]),
     "psgd_topk_workspace_ints": (i32, []),
     "psgd_topk_abs": (i32, [vp, i64, i64, vp, vp, vp, vp, vp]),
+    "psgd_sparse_combine_max_segments": (i32, []),
+    "psgd_sparse_combine_launch": (i32, [vp, vp, i32, i64, vp, i32, f32, vp, vp, vp]),
     "psgd_svd_tall_max_cols": (i32, []),
     "psgd_svd_tall_launch": (i32, [vp, i32, vp, vp, vp, vp, vp]),
     "psgd_bulk_chunk_floats": (i64, []),

@@ -46,3 +46,69 @@ def topk_abs(x: torch.Tensor, k: int, memory: Optional[torch.Tensor] = None) -> 
         memory.copy_(x)
         memory.view(-1)[idx] = 0.0
     return values, idx.to(torch.int32)
+
+
+_SEG_DTYPE = None
+_combine_scratch = {}
+
+
+def sparse_combine(all_values: torch.Tensor, all_positions: torch.Tensor, outs, ends, divisor: float) -> None:
+    """outs[s] <- sum over workers of value / divisor of the (value, position) pairs of segment s, scattered.
+
+    `all_values` / `all_positions`: [workers, K] float32 / int32 (rows as all-gathered); segment s
+    owns columns [ends[s-1], ends[s]) of every row, its positions index into the flattened
+    `outs[s]`. Positions are unique within a row's segment. On CUDA one cooperative launch zeroes
+    the outputs and applies the workers in rank order (csrc/topk.cu), so replicas stay
+    bit-identical; elsewhere the same sum runs as one `index_add_` per worker
+    (gradient_reducers.py:262-271)."""
+    global _SEG_DTYPE
+    workers, per_worker = all_values.shape
+    use_native = (
+        all_values.is_cuda and native.use_for_cuda() and all_values.dtype == torch.float32 and all_positions.dtype == torch.int32
+        and all_values.is_contiguous() and all_positions.is_contiguous()
+        and all(o.is_contiguous() and o.dtype == torch.float32 for o in outs)
+    )
+    if use_native:
+        import numpy as np
+
+        lib = native.lib()
+        cap = int(lib.psgd_sparse_combine_max_segments())
+        if _SEG_DTYPE is None:
+            _SEG_DTYPE = np.dtype([("out", np.uint64), ("numel", np.int64), ("end", np.int64)])
+        device = all_values.device
+        scratch = _combine_scratch.get(device)
+        if scratch is None:
+            scratch = torch.zeros(2, dtype=torch.int32, device=device)  # [grid barrier, status]
+            _combine_scratch[device] = scratch
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for first in range(0, len(outs), cap):
+            chunk = list(range(first, min(first + cap, len(outs))))
+            segs = np.zeros(len(chunk), dtype=_SEG_DTYPE)
+            base = ends[first - 1] if first else 0
+            for j, s in enumerate(chunk):
+                segs[j] = (outs[s].data_ptr(), outs[s].numel(), ends[s] - base)
+            segs_dev = torch.from_numpy(segs.view(np.uint8)).to(device, non_blocking=False)
+            width = ends[chunk[-1]] - base
+            vals = all_values if (base == 0 and width == per_worker) else all_values[:, base : base + width].contiguous()
+            poss = all_positions if (base == 0 and width == per_worker) else all_positions[:, base : base + width].contiguous()
+            code = lib.psgd_sparse_combine_launch(
+                ctypes.c_void_p(vals.data_ptr()), ctypes.c_void_p(poss.data_ptr()), int(workers), ctypes.c_longlong(width),
+                ctypes.c_void_p(segs_dev.data_ptr()), len(chunk), ctypes.c_float(divisor),
+                ctypes.c_void_p(scratch.data_ptr()), ctypes.c_void_p(scratch.data_ptr() + 4), stream,
+            )
+            native.check(code, "psgd_sparse_combine_launch")
+            segs_dev.record_stream(torch.cuda.current_stream())
+        return
+    start = 0
+    for out, end in zip(outs, ends):
+        out.zero_()
+        flat = out.view(-1)
+        for w in range(workers):
+            flat.index_add_(0, all_positions[w, start:end].long(), all_values[w, start:end] / divisor)
+        start = end
+
+
+def sparse_combine_status(device) -> int:
+    """0 unless a grid barrier of `sparse_combine` gave up on `device` (reads the device word: synchronises)."""
+    scratch = _combine_scratch.get(torch.device(device))
+    return 0 if scratch is None else int(scratch[1].item())

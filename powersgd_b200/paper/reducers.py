@@ -33,7 +33,7 @@ import torch.distributed as dist
 from ..orthogonalization import gram_schmidt_
 from ..ops import signpack
 from ..ops.svd import svd_many
-from ..ops.topk import topk_abs
+from ..ops.topk import sparse_combine, topk_abs
 from ..utils import TensorBuffer, n_bits
 from ..utils.timer import Timer
 
@@ -80,6 +80,18 @@ def _gather_all(tensor: torch.Tensor, workers: int) -> List[torch.Tensor]:
     outs = [torch.empty_like(tensor) for _ in range(workers)]
     dist.all_gather(outs, tensor)
     return outs
+
+
+def _rows(gathered: List[torch.Tensor]) -> torch.Tensor:
+    """[workers, K] tensor over the per-worker results of `_gather_all` (no copy when they already
+    are the rows of one gathered buffer, as the in-kernel all-gather returns them)."""
+    first = gathered[0]
+    base = first._base if first._base is not None else None
+    if base is not None and base.dim() == 2 and base.shape == (len(gathered), first.numel()) and all(
+        g._base is base and g.data_ptr() == base.data_ptr() + r * first.numel() * first.element_size() for r, g in enumerate(gathered)
+    ):
+        return base
+    return torch.stack([g.reshape(-1) for g in gathered])
 
 
 def reduce_mean_list(device, list_in: Sequence[torch.Tensor], list_out: Sequence[torch.Tensor], timer) -> int:
@@ -486,11 +498,8 @@ class TopKReducer(Reducer):
             all_positions = _gather_all(positions, self.n_workers)
             bits = n_bits(values) + n_bits(positions)
         with self.timer("reduce.combine", verbosity=2):
-            for out, lo, hi in zip(grad_out, starts, ends):
-                out.zero_()
-                flat = out.view(-1)
-                for pos, val in zip(all_positions, all_values):
-                    flat.index_add_(0, pos[lo:hi].long(), val[lo:hi] / self.n_workers)
+            # zero fill + the scatter of every worker's pairs, in rank order: one launch on CUDA
+            sparse_combine(_rows(all_values), _rows(all_positions), grad_out, ends, float(self.n_workers))
         return bits
 
 
@@ -509,18 +518,18 @@ class GlobalTopKReducer(Reducer):
         with self.timer("reduce.topk", verbosity=2):
             residual = torch.empty_like(flat)
             values, positions = topk_abs(flat, k, memory=residual)
-            positions = positions.long()
         with self.timer("reduce.set_memory", verbosity=2):
             packed.buffer = residual
             packed.unpack(memory_out)
         with self.timer("reduce.reduce", verbosity=2):
             all_values = _gather_all(values, self.n_workers)
             all_positions = _gather_all(positions, self.n_workers)
-            bits = n_bits(values) + n_bits(positions)
+            # positions travel as int32 here; the count keeps the original's int64 convention
+            # (gradient_reducers.py:326-331) so that reported volumes stay comparable
+            bits = n_bits(values) + 64 * positions.nelement()
         with self.timer("reduce.combine", verbosity=2):
-            total = torch.zeros_like(flat)
-            for pos, val in zip(all_positions, all_values):
-                total.index_add_(0, pos, val / self.n_workers)
+            total = torch.empty_like(flat)
+            sparse_combine(_rows(all_values), _rows(all_positions), [total], [k], float(self.n_workers))
             packed.buffer = total
             packed.unpack(grad_out)
         return bits

@@ -306,6 +306,21 @@ def native_all_gather(tensor: torch.Tensor, group=None) -> List[torch.Tensor]:
     return [out[r].view(tensor.shape) for r in range(ch.world)]
 
 
+def native_all_reduce_(tensor: torch.Tensor, group=None) -> torch.Tensor:
+    """In-place SUM all-reduce of a small contiguous float32 CUDA tensor through the one-launch
+    in-kernel collective (the channel is shared with `native_all_gather`). Collective."""
+    device = tensor.device
+    n = tensor.numel()
+    ch = _gather_channels.get(device)
+    if ch is None or ch.cap < n:
+        if ch is not None:
+            ch.close()
+        ch = Channel(max(n, 1 << 16), group)
+        _gather_channels[device] = ch
+    ch.check()
+    return ch.all_reduce_(tensor)
+
+
 def close_gather_channels() -> None:
     """Release the cached all-gather channels (collective across ranks)."""
     for ch in list(_gather_channels.values()):

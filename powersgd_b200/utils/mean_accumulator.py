@@ -1,6 +1,7 @@
 """Running means over nested containers (paper-code/mean_accumulator.py:5-98)."""
 from __future__ import annotations
 
+import os
 from copy import deepcopy
 
 import torch
@@ -15,7 +16,7 @@ class MeanAccumulator:
     """Weighted running mean of floats, tensors, or dicts / lists of them.
 
     `update_weight > 1` biases the mean towards recent samples, as in the harness. `reduce()`
-    merges the accumulators of all workers (count-weighted) with two async all-reduces.
+    merges the accumulators of all workers (count-weighted) with one all-reduce over all leaves.
     """
 
     def __init__(self, update_weight: float = 1):
@@ -73,31 +74,62 @@ class MeanAccumulator:
         else:
             raise ValueError(f"cannot average values of type {type(self.average)}")
 
-    def reduce(self) -> None:
-        if _world() == 1:
-            return
+    def _leaves(self, out: list) -> None:
+        """Leaf accumulators of this tree in a deterministic order (dict keys sorted)."""
         if isinstance(self.average, dict):
             for key in sorted(self.average):
-                self.average[key].reduce()
-            return
-        if isinstance(self.average, list):
+                self.average[key]._leaves(out)
+        elif isinstance(self.average, list):
             for child in self.average:
-                child.reduce()
+                child._leaves(out)
+        else:
+            out.append(self)
+
+    def reduce(self) -> None:
+        """Merges the accumulators of all workers, count-weighted. The original issues two
+        all-reduces per leaf (mean_accumulator.py:67-98); here every leaf's count and weighted sum
+        sit in ONE float32 buffer that is summed once: by the one-launch in-kernel all-reduce on
+        CUDA, by the library collective elsewhere."""
+        if _world() == 1:
             return
-        device = "cuda" if dist.get_backend() == "nccl" else "cpu"
-        count = torch.tensor(float(self.counter), dtype=torch.float32, device=device)
-        h_count = dist.all_reduce(count, async_op=True)
-        if isinstance(self.average, torch.Tensor):
-            weighted = self.average.detach().clone().to(device)
-        else:
-            weighted = torch.tensor(float(self.average), dtype=torch.float32, device=device)
-        weighted.mul_(self.counter)
-        h_sum = dist.all_reduce(weighted, async_op=True)
-        h_count.wait()
-        h_sum.wait()
-        self.counter = count.item()
-        merged = weighted / count
-        if isinstance(self.average, torch.Tensor):
-            self.average = merged.to(self.average.device)
-        else:
-            self.average = merged.item()
+        leaves: list = []
+        self._leaves(leaves)
+        leaves = [leaf for leaf in leaves if leaf.average is not None]
+        if not leaves:
+            return
+        on_gpu = dist.get_backend() == "nccl"
+        device = torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu")
+        parts = []
+        for leaf in leaves:
+            if isinstance(leaf.average, torch.Tensor):
+                value = leaf.average.detach().to(device=device, dtype=torch.float32).reshape(-1) * float(leaf.counter)
+            else:
+                value = torch.tensor([float(leaf.average) * float(leaf.counter)], dtype=torch.float32, device=device)
+            parts.append(torch.tensor([float(leaf.counter)], dtype=torch.float32, device=device))
+            parts.append(value)
+        flat = torch.cat(parts)
+        done = False
+        if on_gpu and os.environ.get("PSGD_B200_COMM", "p2p") == "p2p":
+            from ..ops import native
+
+            if native.use_for_cuda():
+                from ..parallel.symm import native_all_reduce_
+
+                native_all_reduce_(flat)
+                done = True
+        if not done:
+            dist.all_reduce(flat)
+        host = flat.cpu() if on_gpu else flat
+        at = 0
+        for leaf in leaves:
+            count = float(host[at])
+            at += 1
+            if isinstance(leaf.average, torch.Tensor):
+                n = leaf.average.numel()
+                merged = flat[at : at + n].view(leaf.average.shape) / count
+                leaf.average = merged.to(leaf.average.device)
+                at += n
+            else:
+                leaf.average = float(host[at]) / count
+                at += 1
+            leaf.counter = count

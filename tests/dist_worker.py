@@ -345,6 +345,87 @@ def scenario_reducers_native():
         print("SCENARIO-OK")
 
 
+def _check_mean_accumulator(rank, world, dev):
+    """Count-weighted merge of nested accumulators with one collective over all leaves."""
+    from powersgd_b200.utils import MeanAccumulator
+
+    acc = MeanAccumulator()
+    # rank r adds r + 1 samples; sample j of rank r is {"loss": r + j, "vec": [r, j, 1], "pair": [r, 2 j]}
+    for j in range(rank + 1):
+        acc.add({"loss": float(rank + j), "vec": torch.tensor([float(rank), float(j), 1.0], device=dev), "pair": [float(rank), 2.0 * j]})
+    acc.reduce()
+    got = acc.value()
+    n_total = sum(r + 1 for r in range(world))
+    want_loss = sum(float(r + j) for r in range(world) for j in range(r + 1)) / n_total
+    want_vec = [sum(float(r) for r in range(world) for j in range(r + 1)) / n_total,
+                sum(float(j) for r in range(world) for j in range(r + 1)) / n_total, 1.0]
+    assert abs(got["loss"] - want_loss) < 1e-5, (got["loss"], want_loss)
+    assert torch.allclose(got["vec"].cpu(), torch.tensor(want_vec), atol=1e-5), (got["vec"], want_vec)
+    assert abs(got["pair"][0] - want_vec[0]) < 1e-5 and abs(got["pair"][1] - 2 * want_vec[1]) < 1e-5, got["pair"]
+    assert abs(acc.average["loss"].counter - n_total) < 1e-6
+
+
+def scenario_mean_accumulator_gloo():
+    rank, world, dev = _init("gloo")
+    _check_mean_accumulator(rank, world, dev)
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
+def scenario_sparse_reducers_native():
+    """Top-k reducers (native select, in-kernel all-gather, cooperative scatter-combine) against the
+    unmodified upstream classes; the metric accumulator on the in-kernel all-reduce."""
+    import contextlib
+    import importlib.util
+
+    import numpy as np
+
+    rank, world, dev = _init("nccl")
+    _check_mean_accumulator(rank, world, dev)
+    path = os.path.join(ROOT, "baseline", "_ref", "paper_code", "gradient_reducers.py")
+    if not os.path.exists(path):
+        if rank == 0:
+            print("SCENARIO-OK (upstream research code not installed: nothing to compare)")
+        return
+    sys.path.insert(0, os.path.dirname(path))
+    spec = importlib.util.spec_from_file_location("_upstream_reducers", path)
+    up = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(up)
+    from powersgd_b200.ops.topk import sparse_combine_status
+    from powersgd_b200.paper import reducers as ours_mod
+
+    class _Timer:
+        def __call__(self, *a, **k):
+            return contextlib.nullcontext()
+
+    shapes = [(64, 3, 3, 3), (64, 64, 3, 3), (130, 650), (300, 1200), (10, 512), (64,), (1000,)]
+    for name in ("TopKReducer", "GlobalTopKReducer"):
+        theirs = getattr(up, name)(random_seed=5, device=dev, timer=_Timer(), compression=0.05)
+        del theirs.precalc_numbers
+        theirs.rng = np.random.RandomState(5)
+        ours = getattr(ours_mod, name)(random_seed=5, device=dev, compression=0.05)
+        g = torch.Generator().manual_seed(200 + rank)
+        for step in range(3):
+            # distinct magnitudes: no ties at the threshold, so both selections agree
+            grads = [torch.randn(s, generator=g).to(dev) for s in shapes]
+            out_a = [torch.full(s, float("nan"), device=dev) for s in shapes]
+            out_b = [torch.zeros(s, device=dev) for s in shapes]
+            mem_a = [torch.full(s, float("nan"), device=dev) for s in shapes]
+            mem_b = [torch.zeros(s, device=dev) for s in shapes]
+            bits_a = ours.reduce([x.clone() for x in grads], out_a, mem_a)
+            bits_b = theirs.reduce([x.clone() for x in grads], out_b, mem_b)
+            torch.cuda.synchronize()
+            assert bits_a == bits_b, (name, step, bits_a, bits_b)
+            for s, x, y, ma, mb in zip(shapes, out_a, out_b, mem_a, mem_b):
+                assert torch.allclose(x, y, atol=1e-6), (name, step, s, (x - y).abs().max().item())
+                assert torch.equal(ma, mb), (name, step, s)
+                assert _same_on_all_ranks(x, world), (name, "outputs differ between ranks")
+        assert sparse_combine_status(dev) == 0
+        dist.barrier()
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
 def scenario_train_step_timeout():
     """A rank stays away from a training step: the others' bounded device-side waits give up, and
     their NEXT call of the training step raises (naming the step) instead of applying an update

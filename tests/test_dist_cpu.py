@@ -22,7 +22,7 @@ def run_scenario(name, nproc=2, timeout=240, env=None):
     return res
 
 
-@pytest.mark.parametrize("name", ["mlp_gloo", "ef_identity_gloo", "ddp_hooks_gloo", "preflight_gloo", "plan_mismatch_gloo"])
+@pytest.mark.parametrize("name", ["mlp_gloo", "ef_identity_gloo", "ddp_hooks_gloo", "preflight_gloo", "plan_mismatch_gloo", "mean_accumulator_gloo"])
 def test_gloo_scenarios(name):
     res = run_scenario(name)
     assert "SCENARIO-OK" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]

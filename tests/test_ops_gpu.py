@@ -3,7 +3,7 @@ import pytest
 import torch
 
 from powersgd_b200.ops import signpack
-from powersgd_b200.ops.topk import topk_abs
+from powersgd_b200.ops.topk import sparse_combine, sparse_combine_status, topk_abs
 
 pytestmark = pytest.mark.gpu
 
@@ -54,6 +54,42 @@ def test_topk_abs_with_ties_and_zeros():
     assert (values.abs() == 2.0).all() and positions.long().unique().numel() == 150
     values, positions = topk_abs(x, 300)
     assert int((values.abs() == 2.0).sum()) == 200 and positions.long().unique().numel() == 300
+
+
+def test_sparse_combine_matches_sequential_index_add_bitwise():
+    """The cooperative scatter-combine launch against one index_add_ per worker in rank order:
+    identical bits (fixed summation order), also where several workers hit the same position."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(7)
+    workers = 5
+    numels = [27 * 64, 1, 650 * 130, 10, 1 << 20]
+    sizes = [max(1, n // 8) for n in numels]
+    ends = torch.tensor(sizes).cumsum(0).tolist()
+    total = ends[-1]
+    values = torch.randn(workers, total, generator=g).to(dev)
+    positions = torch.empty(workers, total, dtype=torch.int32)
+    start = 0
+    for n, k, end in zip(numels, sizes, ends):
+        for w in range(workers):
+            positions[w, start:end] = torch.randperm(n, generator=g)[:k].to(torch.int32)   # unique per worker, collisions across workers
+        start = end
+    positions = positions.to(dev)
+    outs = [torch.full((n,), float("nan"), device=dev) for n in numels]
+    sparse_combine(values, positions, outs, ends, float(workers))
+    torch.cuda.synchronize()
+    assert sparse_combine_status(dev) == 0
+    start = 0
+    for n, out, end in zip(numels, outs, ends):
+        ref = torch.zeros(n, device=dev)
+        for w in range(workers):
+            ref.index_add_(0, positions[w, start:end].long(), values[w, start:end] / workers)
+        assert torch.allclose(out, ref, atol=1e-6), (n, (out - ref).abs().max().item())
+        assert torch.equal(out, ref), (n, "same sum, different rounding")
+        start = end
+    # a second call reuses the barrier word
+    sparse_combine(values, positions, outs, ends, 1.0)
+    torch.cuda.synchronize()
+    assert sparse_combine_status(dev) == 0 and bool(torch.isfinite(outs[-1]).all())
 
 
 def test_batched_tall_svd_matches_torch():
