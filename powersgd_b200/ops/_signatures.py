@@ -66,6 +66,8 @@ _OPTIONAL = {
     "psgd_bulk_arena_bytes": (i64, [i64, i32]),
     "psgd_bulk_allreduce_launch": (i32, [vp, i64, i32, vp]),
     "psgd_bulk_finish_launch": (i32, [vp, i64, i32, vp]),
+    "psgd_nvls_allreduce_fused_launch": (i32, [vp, vp, i64, i32, i32, vp]),
+    "psgd_nvls_allreduce_launch": (i32, [vp, i64, i32, i32, i32, vp]),
     "psgd_read_pass_launch": (i32, [vp, i64, vp, i32, vp]),
     "psgd_finalize_uses_strip": (i32, [i32, i32, i32, i32]),
     "psgd_symm_alloc": (i32, [C.c_size_t, C.POINTER(vp)]),

@@ -30,6 +30,7 @@ config = dict(
     message_sizes=[4 ** i for i in range(1, 15)],  # bytes: 4 ... 268 435 456
     repetitions=4,
     in_kernel_limit_bytes=4 << 20,  # largest message given to the one-shot peer all-reduce
+    nvls_from_bytes=1 << 20,        # smallest message given to the in-switch (multimem) all-reduce
 )
 
 output_dir = "./output.tmp"
@@ -105,6 +106,7 @@ def main():
         except Exception as exc:  # library not built: NCCL numbers only
             metric("in_kernel_allreduce_unavailable", {"value": 0.0}, {"reason": str(exc)[:80]})
 
+    nvls_ok = [os.environ.get("PSGD_B200_TIMINGS_NVLS", "1") != "0"]
     for size in config["message_sizes"]:
         data = torch.randn(max(size // 4, 1), device=device)
         for _ in range(reps):
@@ -122,6 +124,20 @@ def main():
                 samples.time(f"in_kernel_all_reduce_{size}", bulk.all_reduce_)
             bulk.check()
             bulk.close()
+        if channel is not None and size >= config["nvls_from_bytes"] and nvls_ok[0]:
+            from ..parallel.nvls import NvlsAllReduce, NvlsUnavailable
+
+            try:
+                nvls = NvlsAllReduce(data.numel())
+            except NvlsUnavailable as exc:
+                nvls_ok[0] = False
+                metric("nvls_allreduce_unavailable", {"value": 0.0}, {"reason": str(exc)[:80]})
+            else:
+                nvls.buffer[: data.numel()].copy_(data)
+                for _ in range(reps):
+                    samples.time(f"nvls_all_reduce_{size}", nvls.all_reduce_)
+                nvls.check()
+                nvls.close()
     for size in config["message_sizes"]:
         data = torch.randn(max(size // 4, 1), device=device)
         outs = [torch.empty_like(data) for _ in range(world)]

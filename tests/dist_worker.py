@@ -426,6 +426,60 @@ def scenario_sparse_reducers_native():
         print("SCENARIO-OK")
 
 
+def scenario_nvls_allreduce():
+    """In-switch all-reduce (multimem kernel between two bounded barriers) against the library
+    all-reduce, directly and as the PSGD_B200_FLAT=nvls path of the flat aggregator. Never part of a
+    failure test: every rank closes the buffer (collective) before leaving."""
+    rank, world, dev = _init("nccl")
+    from powersgd_b200.parallel.nvls import NvlsAllReduce, NvlsUnavailable
+
+    g = torch.Generator().manual_seed(300 + rank)
+    for fused in ("1", "0"):   # barriers inside the launch / as two token all-reduces around it
+        os.environ["PSGD_B200_NVLS_FUSED"] = fused
+        try:
+            red = NvlsAllReduce(3 * 1000 * 1000 + 5)
+        except NvlsUnavailable as exc:
+            if rank == 0:
+                print(f"SCENARIO-OK (no NVLink multicast here: {exc})")
+            return
+        assert red.launches == (1 if fused == "1" else 3)
+        for step in range(3):
+            data = torch.randn(red.n_pad, generator=g).to(dev)
+            red.buffer.copy_(data)
+            red.all_reduce_()
+            want = data.clone()
+            dist.all_reduce(want)
+            torch.cuda.synchronize()
+            red.check()
+            assert _rel(red.buffer, want) < 1e-6, (fused, step, _rel(red.buffer, want))
+            assert _same_on_all_ranks(red.buffer, world), "replicas differ"
+        red.close()
+    del os.environ["PSGD_B200_NVLS_FUSED"]
+    # the flat aggregator on the same path
+    os.environ["PSGD_B200_FLAT"] = "nvls"
+    from powersgd_b200.cuda_path import NativeFlatAllReduce
+
+    flat = NativeFlatAllReduce()
+    shapes = [(1000, 700), (300, 1200), (513,), (64, 3, 3, 3)]
+    for step in range(2):
+        grads = [torch.randn(s, generator=g).to(dev) for s in shapes]
+        want = [x.clone() for x in grads]
+        for w in want:
+            dist.all_reduce(w)
+            w.div_(world)
+        got = flat.aggregate(grads)
+        torch.cuda.synchronize()
+        assert flat.path == "nvls", flat.path
+        for a, b in zip(got, want):
+            assert _rel(a, b) < 1e-6, (step, tuple(a.shape), _rel(a, b))
+            assert _same_on_all_ranks(a, world)
+    flat.close()
+    del os.environ["PSGD_B200_FLAT"]
+    dist.barrier()
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
 def scenario_train_step_timeout():
     """A rank stays away from a training step: the others' bounded device-side waits give up, and
     their NEXT call of the training step raises (naming the step) instead of applying an update
