@@ -354,6 +354,11 @@ def main():
 
                         flat_ms, _, _ = time_aggregate(_Flat, grads, args.steps, args.warmup, flush, world, device)
                         row["uncompressed_peer_store_allreduce_ms"] = flat_ms
+                        if ref is not None:
+                            # the upstream package's own uncompressed aggregator: pack (torch.cat), NCCL
+                            # all-reduce, divide, unpack - the like-for-like of the line above
+                            up_ms, _, _ = time_aggregate(lambda: ref.powersgd.AllReduce(), grads, args.steps, args.warmup, flush, world, device)
+                            row["uncompressed_upstream_aggregator_ms"] = up_ms
                 if rank == 0:
                     print(json.dumps(row), flush=True)
         del grads, flush
