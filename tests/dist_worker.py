@@ -480,6 +480,41 @@ def scenario_nvls_allreduce():
         print("SCENARIO-OK")
 
 
+def scenario_paper_train_native():
+    """The research training loop on GPUs (one rank each) for every family of reducers, a few
+    batches of ResNet-18 on synthetic CIFAR: the native select / sign / low-rank / scatter-combine
+    kernels, the in-kernel all-gather and all-reduce and the metric accumulator under a real model.
+    Parameters stay bit-identical across ranks and finite."""
+    import tempfile
+
+    from powersgd_b200.paper import train
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    base = dict(train.config)
+    cases = [("RankKReducer", dict(optimizer_reducer_rank=2)), ("HalfRankKReducer", dict(optimizer_reducer_rank=2)),
+             ("ExactReducer", {}), ("TopKReducer", dict(optimizer_reducer_compression=0.01)),
+             ("GlobalTopKReducer", dict(optimizer_reducer_compression=0.01)), ("SignSGDwithMajorityVoteReducer", {}),
+             ("SignAndNormReducer", {}), ("RandomSparseReducer", dict(optimizer_reducer_rank=2))]
+    for name, extra in cases:
+        train.config.clear()
+        train.config.update(base)
+        train.config.update(num_epochs=1, optimizer_batch_size=32, max_batches_per_epoch=3, log_verbosity=0, train_size=512, test_size=64,
+                            task_architecture="ResNet18", distributed_backend="nccl", optimizer_scale_lr_with_warmup_epochs=0,
+                            optimizer_learning_rate=0.01, optimizer_conv_learning_rate=0.01, optimizer_reducer=name, **extra)
+        train.output_dir = tempfile.mkdtemp(prefix=f"psgd_{name}_")
+        task, reducer, bits = train.main()
+        dev = task.state[0].device
+        torch.cuda.synchronize()
+        assert bits > 0, name
+        for p in task.state:
+            assert bool(torch.isfinite(p).all()), name
+        flat = torch.cat([p.detach().reshape(-1).float() for p in task.state])
+        assert _same_on_all_ranks(flat, world), (name, "replicas diverged")
+        dist.barrier()
+    if rank == 0:
+        print("SCENARIO-OK")
+
+
 def scenario_train_step_timeout():
     """A rank stays away from a training step: the others' bounded device-side waits give up, and
     their NEXT call of the training step raises (naming the step) instead of applying an update

@@ -12,7 +12,7 @@ ENV = {"NCCL_NVLS_ENABLE": "0"}
 
 
 @needs_two
-@pytest.mark.parametrize("name", ["channel_allreduce", "flat_twoshot", "powersgd_native", "train_step_graph", "channel_timeout", "preflight", "reducers_native", "sparse_reducers_native", "nvls_allreduce"])
+@pytest.mark.parametrize("name", ["channel_allreduce", "flat_twoshot", "powersgd_native", "train_step_graph", "channel_timeout", "preflight", "reducers_native", "sparse_reducers_native", "nvls_allreduce", "paper_train_native"])
 def test_two_gpu_scenarios(name):
     res = run_scenario(name, nproc=2, timeout=600, env=ENV)
     assert "SCENARIO-OK" in res.stdout, res.stdout[-3000:] + res.stderr[-6000:]
