@@ -125,6 +125,176 @@ PSGD_API int psgd_topk_abs(const float* x, long long n, long long k, int* worksp
 }
 
 // ---------------------------------------------------------------------------------------------
+// The same selection for MANY tensors at once. The per-tensor reducer of the harness calls the
+// selection once per parameter (62 times for ResNet-18, paper-code/gradient_reducers.py:226-253),
+// which is launch-bound; here the three histogram passes and the compaction are four launches for
+// the whole list. Every block serves one (tensor, chunk) pair from a block table; every tensor has
+// its own histograms and counters in the workspace, and the digit is chosen by the whole block
+// with a parallel suffix scan instead of one thread walking the bins.
+namespace {
+
+struct TopkItem {
+  const float* x;      // tensor, n entries
+  float* memory;       // optional: x with the taken entries zeroed
+  long long n;
+  long long k;         // entries to take (1 <= k <= n)
+  long long out_off;   // start of this tensor's k pairs in values / positions
+};
+
+// Block-wide: walks `bins` (<= 2048, TK_THREADS threads x 4 bins) from the top until `remain` entries are
+// covered; returns the bin in *bin_out and the number to take inside it in *remain_io. `scan` is
+// TK_THREADS ints of shared memory.
+__device__ void tk_choose_block(const int* __restrict__ hist, int bins, long long* remain_io, int* bin_out, int* scan) {
+  const int t = threadIdx.x;
+  // thread t owns bins [4t, 4t + 4), counted from the TOP: bin index bins - 1 - j
+  int c[4], local = 0;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int j = 4 * t + u;
+    c[u] = j < bins ? hist[bins - 1 - j] : 0;
+    local += c[u];
+  }
+  scan[t] = local;
+  __syncthreads();
+  // inclusive prefix sum over the TK_THREADS partials (Hillis-Steele; 9 rounds)
+  for (int off = 1; off < TK_THREADS; off <<= 1) {
+    const int v = t >= off ? scan[t - off] : 0;
+    __syncthreads();
+    scan[t] += v;
+    __syncthreads();
+  }
+  const long long remain = *remain_io;
+  const long long before = t == 0 ? 0 : scan[t - 1];   // entries in the bins above this thread's
+  __syncthreads();
+  if (before < remain && remain <= before + local) {    // exactly one thread
+    long long left = remain - before;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (left <= c[u]) {
+        *bin_out = bins - 1 - (4 * t + u);
+        *remain_io = left;
+        break;
+      }
+      left -= c[u];
+    }
+  }
+  __syncthreads();
+}
+
+// Digits chosen so far for one tensor (block-wide; result in shared `pick`).
+__device__ void tk_derive_block(const int* ws, int upto, long long k, Pick* pick, long long* remain_sh, int* bin_sh, int* scan) {
+  if (threadIdx.x == 0) {
+    pick->prefix = 0u;
+    *remain_sh = k;
+    *bin_sh = 0;
+  }
+  __syncthreads();
+  if (upto >= 1) {
+    tk_choose_block(ws, TK_BINS0, remain_sh, bin_sh, scan);
+    if (threadIdx.x == 0) pick->prefix |= (unsigned)(*bin_sh) << 20;
+    __syncthreads();
+  }
+  if (upto >= 2) {
+    tk_choose_block(ws + TK_BINS0, TK_BINS1, remain_sh, bin_sh, scan);
+    if (threadIdx.x == 0) pick->prefix |= (unsigned)(*bin_sh) << 9;
+    __syncthreads();
+  }
+  if (upto >= 3) {
+    tk_choose_block(ws + TK_BINS0 + TK_BINS1, TK_BINS2, remain_sh, bin_sh, scan);
+    if (threadIdx.x == 0) pick->prefix |= (unsigned)(*bin_sh);
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) pick->remain = *remain_sh;
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(TK_THREADS) psgd_topk_many_hist_kernel(const TopkItem* __restrict__ items, const int* __restrict__ block_item,
+                                                                          const int* __restrict__ block_part, const int* __restrict__ item_parts,
+                                                                          int* __restrict__ ws_all, int pass) {
+  __shared__ int sh[TK_BINS0];
+  __shared__ int scan[TK_THREADS];
+  __shared__ Pick pick;
+  __shared__ long long remain_sh;
+  __shared__ int bin_sh;
+  const int it = block_item[blockIdx.x];
+  const TopkItem item = items[it];
+  int* ws = ws_all + (long long)it * TK_WS_INTS;
+  const int bins = pass == 2 ? TK_BINS2 : TK_BINS0;
+  for (int b = threadIdx.x; b < bins; b += TK_THREADS) sh[b] = 0;
+  tk_derive_block(ws, pass, item.k, &pick, &remain_sh, &bin_sh, scan);
+  const unsigned prefix = pick.prefix;
+  const unsigned mask = pass == 0 ? 0u : (pass == 1 ? 0x7FF00000u : 0x7FFFFE00u);
+  const int shift = pass == 0 ? 20 : (pass == 1 ? 9 : 0);
+  const unsigned digit_mask = pass == 2 ? 0x1FFu : 0x7FFu;
+  const long long stride = (long long)item_parts[it] * TK_THREADS;
+  for (long long i = (long long)block_part[blockIdx.x] * TK_THREADS + threadIdx.x; i < item.n; i += stride) {
+    const unsigned key = tk_key(__ldg(item.x + i));
+    if ((key & mask) == prefix) atomicAdd(&sh[(key >> shift) & digit_mask], 1);
+  }
+  __syncthreads();
+  int* hist = ws + (pass == 0 ? 0 : (pass == 1 ? TK_BINS0 : TK_BINS0 + TK_BINS1));
+  for (int b = threadIdx.x; b < bins; b += TK_THREADS)
+    if (sh[b]) atomicAdd(hist + b, sh[b]);
+}
+
+__global__ void __launch_bounds__(TK_THREADS) psgd_topk_many_compact_kernel(const TopkItem* __restrict__ items, const int* __restrict__ block_item,
+                                                                             const int* __restrict__ block_part, const int* __restrict__ item_parts,
+                                                                             int* __restrict__ ws_all, float* __restrict__ values,
+                                                                             int* __restrict__ positions) {
+  __shared__ int scan[TK_THREADS];
+  __shared__ Pick pick;
+  __shared__ long long remain_sh;
+  __shared__ int bin_sh;
+  const int it = block_item[blockIdx.x];
+  const TopkItem item = items[it];
+  int* ws = ws_all + (long long)it * TK_WS_INTS;
+  tk_derive_block(ws, 3, item.k, &pick, &remain_sh, &bin_sh, scan);
+  const unsigned threshold = pick.prefix;
+  const long long take_equal = pick.remain;
+  const long long base_equal = item.k - take_equal;
+  int* cnt_gt = ws + TK_BINS0 + TK_BINS1 + TK_BINS2;
+  int* cnt_eq = cnt_gt + 1;
+  float* val = values + item.out_off;
+  int* pos = positions + item.out_off;
+  const long long stride = (long long)item_parts[it] * TK_THREADS;
+  for (long long i = (long long)block_part[blockIdx.x] * TK_THREADS + threadIdx.x; i < item.n; i += stride) {
+    const float v = __ldg(item.x + i);
+    const unsigned key = tk_key(v);
+    long long slot = -1;
+    if (key > threshold) slot = atomicAdd(cnt_gt, 1);
+    else if (key == threshold) {
+      const long long e = atomicAdd(cnt_eq, 1);
+      if (e < take_equal) slot = base_equal + e;
+    }
+    if (slot >= 0) {
+      val[slot] = v;
+      pos[slot] = (int)i;
+    }
+    if (item.memory) item.memory[i] = slot >= 0 ? 0.f : v;
+  }
+}
+
+}  // namespace
+
+PSGD_API int psgd_topk_item_bytes() { return (int)sizeof(TopkItem); }
+
+// Top-k of |x| for `nitems` tensors in four launches. items: device array of TopkItem; block_item /
+// block_part: device tables of `nblocks` entries (which tensor a block serves and which of that
+// tensor's `item_parts[item]` interleaved parts); workspace: nitems * psgd_topk_workspace_ints() ints.
+// values / positions receive every tensor's k pairs at its `out_off`.
+PSGD_API int psgd_topk_abs_many(const void* items, int nitems, const int* block_item, const int* block_part, const int* item_parts,
+                                int nblocks, int* workspace, float* values, int* positions, cudaStream_t stream) {
+  if (nitems <= 0 || nblocks <= 0) return 0;
+  PSGD_CUDA_OK(cudaMemsetAsync(workspace, 0, sizeof(int) * (size_t)TK_WS_INTS * nitems, stream));
+  const TopkItem* it = (const TopkItem*)items;
+  for (int pass = 0; pass < 3; ++pass)
+    psgd_topk_many_hist_kernel<<<nblocks, TK_THREADS, 0, stream>>>(it, block_item, block_part, item_parts, workspace, pass);
+  psgd_topk_many_compact_kernel<<<nblocks, TK_THREADS, 0, stream>>>(it, block_item, block_part, item_parts, workspace, values, positions);
+  PSGD_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Combine step of the top-k reducers: after the all-gather every worker holds W lists of
 // (value, position) pairs and adds value / W into dense, zeroed outputs
 // (paper-code/gradient_reducers.py:262-271 and 333-339 do it with one index_add_ per worker).

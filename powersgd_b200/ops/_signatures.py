@@ -58,6 +58,8 @@ _OPTIONAL = {
     "psgd_finalize_tc_launch": (i32, [vp, vp, i32, vp, vp, i32, i32, vp, vp, vp, vp, f32, i32, vp, vp]),
     "psgd_topk_workspace_ints": (i32, []),
     "psgd_topk_abs": (i32, [vp, i64, i64, vp, vp, vp, vp, vp]),
+    "psgd_topk_item_bytes": (i32, []),
+    "psgd_topk_abs_many": (i32, [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp]),
     "psgd_sparse_combine_max_segments": (i32, []),
     "psgd_sparse_combine_launch": (i32, [vp, vp, i32, i64, vp, i32, f32, vp, vp, vp]),
     "psgd_svd_tall_max_cols": (i32, []),
@@ -66,6 +68,14 @@ _OPTIONAL = {
     "psgd_bulk_arena_bytes": (i64, [i64, i32]),
     "psgd_bulk_allreduce_launch": (i32, [vp, i64, i32, vp]),
     "psgd_bulk_finish_launch": (i32, [vp, i64, i32, vp]),
+    "psgd_mc_buffer_bytes": (i32, []),
+    "psgd_mc_supported": (i32, []),
+    "psgd_mc_round_up": (i32, [i32, C.c_ulonglong, vp]),
+    "psgd_mc_create": (i32, [i32, C.c_ulonglong, vp, vp]),
+    "psgd_mc_import": (i32, [i32, C.c_ulonglong, vp]),
+    "psgd_mc_add_device": (i32, [vp]),
+    "psgd_mc_bind": (i32, [vp]),
+    "psgd_mc_release": (i32, [vp]),
     "psgd_nvls_allreduce_fused_launch": (i32, [vp, vp, i64, i32, i32, vp]),
     "psgd_nvls_allreduce_launch": (i32, [vp, i64, i32, i32, i32, vp]),
     "psgd_read_pass_launch": (i32, [vp, i64, vp, i32, vp]),

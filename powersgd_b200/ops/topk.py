@@ -48,6 +48,79 @@ def topk_abs(x: torch.Tensor, k: int, memory: Optional[torch.Tensor] = None) -> 
     return values, idx.to(torch.int32)
 
 
+_many_cache: dict = {}
+
+
+def topk_abs_many(tensors, ks, memories=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """`topk_abs` for a list of tensors in four launches (csrc/topk.cu, psgd_topk_abs_many).
+
+    Returns flat `(values, positions)`: tensor i's `ks[i]` pairs start at `sum(ks[:i])`; positions
+    are int32 indices into the flattened tensor i. `memories[i]`, when given, receives tensor i with
+    the taken entries zeroed. Falls back to one `topk_abs` per tensor off the GPU."""
+    ks = [int(k) for k in ks]
+    total = sum(ks)
+    flats = [t.reshape(-1) for t in tensors]
+    mems = list(memories) if memories is not None else [None] * len(flats)
+    device = flats[0].device
+    native_ok = (
+        device.type == "cuda" and native.use_for_cuda()
+        and all(t.dtype == torch.float32 and t.is_contiguous() for t in tensors)   # flats are then views
+        and all(m is None or (m.is_contiguous() and m.dtype == torch.float32) for m in mems)
+    )
+    if not native_ok:
+        values = torch.empty(total, dtype=torch.float32, device=device)
+        positions = torch.empty(total, dtype=torch.int32, device=device)
+        at = 0
+        for t, k, m in zip(tensors, ks, mems):
+            v, p = topk_abs(t, k, memory=m)
+            values[at : at + k], positions[at : at + k] = v, p
+            at += k
+        return values, positions
+    import numpy as np
+
+    lib = native.lib()
+    key = (device, tuple(f.data_ptr() for f in flats), tuple(0 if m is None else m.data_ptr() for m in mems), tuple(f.numel() for f in flats), tuple(ks))
+    entry = _many_cache.get(key)
+    if entry is None:
+        dtype = np.dtype([("x", np.uint64), ("memory", np.uint64), ("n", np.int64), ("k", np.int64), ("out_off", np.int64)])
+        if dtype.itemsize != int(lib.psgd_topk_item_bytes()):
+            raise RuntimeError("top-k item record out of sync with the native library")
+        items = np.zeros(len(flats), dtype=dtype)
+        block_item, block_part, parts = [], [], []
+        at = 0
+        for i, (f, k, m) in enumerate(zip(flats, ks, mems)):
+            n = f.numel()
+            if not (0 < k <= n < (1 << 31)):
+                raise ValueError(f"topk_abs_many: need 0 < k <= n < 2^31 (k = {k}, n = {n})")
+            items[i] = (f.data_ptr(), 0 if m is None else m.data_ptr(), n, k, at)
+            at += k
+            nparts = max(1, min(64, -(-n // (512 * 8))))
+            parts.append(nparts)
+            block_item += [i] * nparts
+            block_part += list(range(nparts))
+        to_dev = lambda a: torch.from_numpy(a.view(np.uint8) if a.dtype.names else a).to(device)  # noqa: E731
+        entry = {
+            "items": to_dev(items), "block_item": to_dev(np.asarray(block_item, dtype=np.int32)),
+            "block_part": to_dev(np.asarray(block_part, dtype=np.int32)), "parts": to_dev(np.asarray(parts, dtype=np.int32)),
+            "nblocks": len(block_item),
+            "ws": torch.zeros(len(flats) * int(lib.psgd_topk_workspace_ints()), dtype=torch.int32, device=device),
+            "keep": (flats, mems),   # the tables hold raw pointers: keep the tensors alive with them
+        }
+        if len(_many_cache) > 8:
+            _many_cache.clear()
+        _many_cache[key] = entry
+    values = torch.empty(total, dtype=torch.float32, device=device)
+    positions = torch.empty(total, dtype=torch.int32, device=device)
+    vp = ctypes.c_void_p
+    code = lib.psgd_topk_abs_many(
+        vp(entry["items"].data_ptr()), len(flats), vp(entry["block_item"].data_ptr()), vp(entry["block_part"].data_ptr()),
+        vp(entry["parts"].data_ptr()), entry["nblocks"], vp(entry["ws"].data_ptr()), vp(values.data_ptr()), vp(positions.data_ptr()),
+        vp(torch.cuda.current_stream().cuda_stream),
+    )
+    native.check(code, "psgd_topk_abs_many")
+    return values, positions
+
+
 _SEG_DTYPE = None
 _combine_scratch = {}
 

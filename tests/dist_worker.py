@@ -434,8 +434,11 @@ def scenario_nvls_allreduce():
     from powersgd_b200.parallel.nvls import NvlsAllReduce, NvlsUnavailable
 
     g = torch.Generator().manual_seed(300 + rank)
-    for fused in ("1", "0"):   # barriers inside the launch / as two token all-reduces around it
+    # barriers inside the launch / as two token all-reduces around it; memory bound by this package's
+    # runtime / by PyTorch's symmetric-memory runtime
+    for fused, runtime in (("1", "native"), ("0", "native"), ("1", "torch")):
         os.environ["PSGD_B200_NVLS_FUSED"] = fused
+        os.environ["PSGD_B200_NVLS_RUNTIME"] = runtime
         try:
             red = NvlsAllReduce(3 * 1000 * 1000 + 5)
         except NvlsUnavailable as exc:
@@ -443,6 +446,7 @@ def scenario_nvls_allreduce():
                 print(f"SCENARIO-OK (no NVLink multicast here: {exc})")
             return
         assert red.launches == (1 if fused == "1" else 3)
+        assert red.runtime == runtime, f"asked for the {runtime} runtime, got {red.runtime}"
         for step in range(3):
             data = torch.randn(red.n_pad, generator=g).to(dev)
             red.buffer.copy_(data)
@@ -454,7 +458,7 @@ def scenario_nvls_allreduce():
             assert _rel(red.buffer, want) < 1e-6, (fused, step, _rel(red.buffer, want))
             assert _same_on_all_ranks(red.buffer, world), "replicas differ"
         red.close()
-    del os.environ["PSGD_B200_NVLS_FUSED"]
+    del os.environ["PSGD_B200_NVLS_FUSED"], os.environ["PSGD_B200_NVLS_RUNTIME"]
     # the flat aggregator on the same path
     os.environ["PSGD_B200_FLAT"] = "nvls"
     from powersgd_b200.cuda_path import NativeFlatAllReduce

@@ -265,6 +265,13 @@ def test_train_step_with_channels_last_weights_matches_plain_loop():
             assert int(ba) == int(bb) == len(batches), name
         else:
             assert _rel(ba, bb) < 2e-3, name
+    # the counters are views of one tensor bumped by a single launch; checkpoints do not notice
+    assert step._norm_counters is not None and step._norm_counters.tolist() == [len(batches)] * 2
+    assert set(ma.state_dict()) == set(mb.state_dict())
+    ma.load_state_dict(mb.state_dict())
+    step(*batches[0])
+    assert step._norm_counters.tolist() == [len(batches) + 1] * 2
+    assert all(int(m.num_batches_tracked) == len(batches) + 1 for m in ma.modules() if isinstance(m, torch.nn.BatchNorm2d))
 
 
 def test_compression_error_matches_upstream_package():

@@ -3,7 +3,7 @@ import pytest
 import torch
 
 from powersgd_b200.ops import signpack
-from powersgd_b200.ops.topk import sparse_combine, sparse_combine_status, topk_abs
+from powersgd_b200.ops.topk import sparse_combine, sparse_combine_status, topk_abs, topk_abs_many
 
 pytestmark = pytest.mark.gpu
 
@@ -54,6 +54,38 @@ def test_topk_abs_with_ties_and_zeros():
     assert (values.abs() == 2.0).all() and positions.long().unique().numel() == 150
     values, positions = topk_abs(x, 300)
     assert int((values.abs() == 2.0).sum()) == 200 and positions.long().unique().numel() == 300
+
+
+def test_topk_abs_many_matches_per_tensor_selection():
+    """One batched call (four launches) against torch.topk per tensor: same value multisets, positions
+    consistent with values, memories = tensors with the taken entries zeroed; repeated calls reuse the
+    cached tables; ties and an all-equal tensor included."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(3)
+    shapes = [(64, 3, 3, 3), (10,), (1,), (512, 4608), (300, 1200), (64,), (130, 650), (2048,)]
+    tensors = [torch.randn(s, generator=g).to(dev) for s in shapes]
+    tensors[5].fill_(1.5)                       # all equal: any subset is a valid answer
+    tensors[7][::2] = tensors[7][1::2]          # pairs of exact ties
+    ks = [max(1, t.numel() // 7) for t in tensors]
+    ks[1], ks[2] = 10, 1                        # k == n
+    for rep in range(2):
+        mems = [torch.full_like(t, float("nan")) for t in tensors] if rep == 0 else mems
+        values, positions = topk_abs_many(tensors, ks, mems)
+        torch.cuda.synchronize()
+        assert values.shape == (sum(ks),) and positions.dtype == torch.int32
+        at = 0
+        for t, k, m in zip(tensors, ks, mems):
+            v, p = values[at : at + k], positions[at : at + k].long()
+            at += k
+            flat = t.reshape(-1)
+            assert p.unique().numel() == k and int(p.min()) >= 0 and int(p.max()) < flat.numel()
+            assert torch.equal(v, flat[p])
+            ref, _ = torch.topk(flat.abs(), k, sorted=True)
+            assert torch.equal(v.abs().sort(descending=True).values, ref)
+            expect = flat.clone()
+            expect[p] = 0.0
+            assert torch.equal(m.reshape(-1), expect)
+        tensors[0].mul_(-1.0)                   # same pointers, new data: the cached tables stay valid
 
 
 def test_sparse_combine_matches_sequential_index_add_bitwise():
