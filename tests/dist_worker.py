@@ -99,6 +99,7 @@ def scenario_flat_twoshot():
     rank, world, dev = _init("nccl")
     from powersgd_b200.cuda_path import NativeCompressor, NativeFlatAllReduce, _to_device
 
+    os.environ["PSGD_B200_FLAT"] = "bulk"   # this scenario is about the two-shot kernels, whatever `auto` would take
     shapes = [(1000, 333), (7,), (513, 1025), (3, 3, 3, 3)]  # odd total: the padded tail is exercised
 
     def alloc(odd):
