@@ -105,3 +105,25 @@ def test_bulk_allreduce_layout_helpers():
     for k, same in ((8, 1), (8, 0), (32, 0), (64, 1)):
         rows = int(lib.psgd_finalize_strip_rows(k, same))
         assert rows % 32 == 0 and 32 <= rows <= 256
+
+
+def test_multicast_runtime_degrades_without_a_driver():
+    """csrc/mcast.cpp looks its driver entry points up at run time: on a machine without a GPU the
+    library still loads, reports no multicast support and refuses politely (error code + message)."""
+    import ctypes
+
+    import torch
+
+    from powersgd_b200.parallel.nvls import _McBuffer
+
+    lib = _lib()
+    assert ctypes.sizeof(_McBuffer) == int(lib.psgd_mc_buffer_bytes())
+    if torch.cuda.is_available():
+        pytest.skip("this check is for driver-less machines")
+    assert int(lib.psgd_mc_supported()) == 0
+    out = ctypes.c_ulonglong(0)
+    assert int(lib.psgd_mc_round_up(2, ctypes.c_ulonglong(1 << 20), ctypes.byref(out))) != 0
+    assert lib.psgd_last_error()
+    state = _McBuffer()
+    assert int(lib.psgd_mc_release(ctypes.byref(state))) == 0   # nothing set up: nothing to undo
+
