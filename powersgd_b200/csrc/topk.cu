@@ -227,6 +227,7 @@ __global__ void __launch_bounds__(TK_THREADS) psgd_topk_many_hist_kernel(const T
   const int shift = pass == 0 ? 20 : (pass == 1 ? 9 : 0);
   const unsigned digit_mask = pass == 2 ? 0x1FFu : 0x7FFu;
   const long long stride = (long long)item_parts[it] * TK_THREADS;
+#pragma unroll 4
   for (long long i = (long long)block_part[blockIdx.x] * TK_THREADS + threadIdx.x; i < item.n; i += stride) {
     const unsigned key = tk_key(__ldg(item.x + i));
     if ((key & mask) == prefix) atomicAdd(&sh[(key >> shift) & digit_mask], 1);

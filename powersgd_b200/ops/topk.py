@@ -94,7 +94,7 @@ def topk_abs_many(tensors, ks, memories=None) -> Tuple[torch.Tensor, torch.Tenso
                 raise ValueError(f"topk_abs_many: need 0 < k <= n < 2^31 (k = {k}, n = {n})")
             items[i] = (f.data_ptr(), 0 if m is None else m.data_ptr(), n, k, at)
             at += k
-            nparts = max(1, min(64, -(-n // (512 * 8))))
+            nparts = max(1, min(256, -(-n // (512 * 8))))   # <= 8 elements per thread and pass up to 1 Mi entries, then longer loops
             parts.append(nparts)
             block_item += [i] * nparts
             block_part += list(range(nparts))
