@@ -104,9 +104,10 @@ def topk_abs_many(tensors, ks, memories=None) -> Tuple[torch.Tensor, torch.Tenso
             "block_part": to_dev(np.asarray(block_part, dtype=np.int32)), "parts": to_dev(np.asarray(parts, dtype=np.int32)),
             "nblocks": len(block_item),
             "ws": torch.zeros(len(flats) * int(lib.psgd_topk_workspace_ints()), dtype=torch.int32, device=device),
-            "keep": (flats, mems),   # the tables hold raw pointers: keep the tensors alive with them
         }
-        if len(_many_cache) > 8:
+        # the tables hold addresses and lengths only, and the key is exactly those: an entry stays
+        # valid for whatever tensors present the same addresses again, so no tensor is kept alive
+        if len(_many_cache) >= 4:
             _many_cache.clear()
         _many_cache[key] = entry
     values = torch.empty(total, dtype=torch.float32, device=device)
