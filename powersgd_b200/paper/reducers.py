@@ -650,26 +650,48 @@ class _SignBase(Reducer):
 
 
 class SignAndNormReducer(_SignBase):
-    """Signs scaled by each tensor's mean absolute value; memory = x - mean|x| sign(x)."""
+    """Signs scaled by each tensor's mean absolute value; memory = x - mean|x| sign(x).
+
+    Same arithmetic as gradient_reducers.py:37-106, arranged on the flat buffer: the per-tensor
+    scales stay on the device and are spread over their tensors' elements with one gather through a
+    cached element-to-tensor index, so a step has no host synchronisation and no per-tensor kernels (the
+    original reads every norm back with `.item()` and issues three kernels per tensor and worker)."""
+
+    _owner_key = None
+
+    def _element_owner(self, grad_in, device):
+        """(index of the tensor every element of the flat buffer belongs to, 1 / numel per tensor);
+        built once per tensor list."""
+        key = (tuple(t.nelement() for t in grad_in), device)
+        if key != self._owner_key:
+            numels = torch.tensor(key[0], device=device)
+            self._owner = torch.repeat_interleave(torch.arange(len(grad_in), device=device, dtype=torch.int32), numels)
+            self._per_element = 1.0 / numels.to(torch.float32)
+            self._owner_key = key
+        return self._owner, self._per_element
 
     def reduce(self, grad_in, grad_out, memory_out) -> int:
+        grad_in = list(grad_in)
         with self.timer("reduce.norms", verbosity=2):
-            norms = torch.stack([t.norm(p=1) for t in grad_in])
+            norms = torch.stack(torch._foreach_norm(grad_in, 1))
         packed, words, size, gathered = self._exchange(grad_in)
         all_norms = _gather_all(norms, self.n_workers)
         bits = n_bits(words) + n_bits(norms)
+        owner, per_element = self._element_owner(grad_in, norms.device)
         with self.timer("reduce.average", verbosity=2):
-            for out in grad_out:
-                out.zero_()
             comp = SignCompressor()
+            mean = torch.zeros_like(packed.buffer)
             for their_words, their_norms in zip(gathered, all_norms):
-                packed.buffer = comp.uncompress(their_words, size)
-                for sign, out, norm in zip(packed, grad_out, their_norms):
-                    out.add_(sign, alpha=float(norm) / sign.nelement() / self.n_workers)
+                scale = torch.index_select(their_norms * per_element / self.n_workers, 0, owner)
+                mean.addcmul_(comp.uncompress(their_words, size).view(-1), scale)
         with self.timer("reduce.memory", verbosity=2):
-            for t, mem, norm in zip(grad_in, memory_out, norms):
-                mem.copy_(t)
-                mem.add_(t.sign(), alpha=-float(norm) / t.nelement())
+            own = torch.index_select(norms * per_element, 0, owner)
+            residual = torch.addcmul(packed.buffer, packed.buffer.sign(), own, value=-1.0)
+            packed.buffer = residual
+            packed.unpack(memory_out)
+        with self.timer("reduce.set_out", verbosity=2):
+            packed.buffer = mean
+            packed.unpack(grad_out)
         return bits
 
 
@@ -680,15 +702,15 @@ class SignReducer(_SignBase):
     def reduce(self, grad_in, grad_out, memory_out) -> int:
         packed, words, size, gathered = self._exchange(grad_in)
         bits = n_bits(words)
+        with self.timer("reduce.memory", verbosity=2):
+            flat = packed.buffer
+            packed.buffer = flat + flat.sign()
+            packed.unpack(memory_out)
         with self.timer("reduce.average", verbosity=2):
             comp = SignCompressor()
             mean = sum(comp.uncompress(w, size) for w in gathered) / self.n_workers
             packed.buffer = mean
             packed.unpack(grad_out)
-        with self.timer("reduce.memory", verbosity=2):
-            for t, mem in zip(grad_in, memory_out):
-                mem.copy_(t)
-                mem.add_(t.sign())
         return bits
 
 

@@ -49,13 +49,15 @@ class TensorBuffer:
             yield self[i]
 
     def pack(self, tensors: Optional[Sequence[torch.Tensor]] = None) -> None:
-        source = self._tensors if tensors is None else tensors
-        for i, t in enumerate(source):
-            self[i].copy_(t)
+        source = list(self._tensors if tensors is None else tensors)
+        if source:
+            # one multi-tensor copy instead of a copy kernel per tensor (62 for ResNet-18)
+            torch._foreach_copy_([self[i] for i in range(len(source))], source)
 
     def unpack(self, tensors: Sequence[torch.Tensor]) -> None:
-        for i, t in enumerate(tensors):
-            t.copy_(self[i])
+        tensors = list(tensors)
+        if tensors:
+            torch._foreach_copy_(tensors, [self[i] for i in range(len(tensors))])
 
     def nelement(self) -> int:
         return self.buffer.nelement()
