@@ -120,6 +120,8 @@ def main():
         "RankKReducer": dict(rank=2, reuse_query=True), "HalfRankKReducer": dict(rank=2), "ExactReducer": {},
         "TopKReducer": dict(compression=1 / 244), "GlobalTopKReducer": dict(compression=1 / 244),
         "SignSGDwithMajorityVoteReducer": {}, "SignAndNormReducer": {}, "SignReducer": {},
+        "RandomSparseReducer": dict(rank=2), "RandomSparseBlockReducer": dict(rank=2),
+        "UniformRandomSparseReducer": dict(compression=1 / 244), "UniformRandomSparseBlockReducer": dict(compression=1 / 244),
     }
     for name in args.reducers.split(","):
         kw = kwargs.get(name, {})

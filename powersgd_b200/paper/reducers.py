@@ -94,6 +94,24 @@ def _rows(gathered: List[torch.Tensor]) -> torch.Tensor:
     return torch.stack([g.reshape(-1) for g in gathered])
 
 
+def _sum_all(tensor: torch.Tensor, workers: int) -> None:
+    """In-place SUM over workers. Small float32 CUDA messages (up to 2^18 floats) go through this
+    package's one-launch in-kernel all-reduce; PSGD_B200_COMM=nccl, larger or other messages go
+    through the library collective."""
+    if workers == 1:
+        return
+    if (tensor.is_cuda and tensor.dtype == torch.float32 and tensor.is_contiguous() and tensor.nelement() <= (1 << 18)
+            and os.environ.get("PSGD_B200_COMM", "p2p") == "p2p"):
+        from ..ops import native
+
+        if native.use_for_cuda():
+            from ..parallel.symm import native_all_reduce_
+
+            native_all_reduce_(tensor)
+            return
+    dist.all_reduce(tensor)
+
+
 def reduce_mean_list(device, list_in: Sequence[torch.Tensor], list_out: Sequence[torch.Tensor], timer) -> int:
     """Mean over workers of a list of tensors through one flat buffer. Returns bits sent
     (0 with a single worker, where the inputs are simply copied)."""
@@ -540,27 +558,38 @@ class _SparseBase(Reducer):
         raise NotImplementedError
 
     def reduce(self, grad_in, grad_out, memory_out) -> int:
-        picks, chunks = [], []
+        """The original works tensor by tensor (a gather, a copy, an indexed store, a zero fill and a
+        scatter per tensor, gradient_reducers.py:350-581). Here the per-tensor picks - drawn in the
+        same order from the shared stream - become ONE index into the flat gradient, so a step is a
+        gather, an indexed zero, an all-reduce, a scatter and two multi-tensor unpacks."""
+        grad_in = list(grad_in)
         with self.timer("reduce.block", verbosity=2):
-            for t in grad_in:
-                idx = self._pick(t, self._budget(t))
-                picks.append(idx)
-                chunks.append(t.reshape(-1)[idx])
+            index = self._pick_all(grad_in)
         with self.timer("reduce.flatpack", verbosity=2):
-            packed = TensorBuffer(chunks)
+            packed = TensorBuffer(grad_in)
+            flat = packed.buffer
+            values = flat[index]
         with self.timer("reduce.memory", verbosity=2):
-            for t, mem, idx in zip(grad_in, memory_out, picks):
-                mem.copy_(t)
-                mem.view(-1)[idx] = 0.0
+            flat[index] = 0.0   # `flat` is a copy of the gradients: what is left is the memory
+            packed.unpack(memory_out)
         with self.timer("reduce.reduce", verbosity=2):
-            packed.all_reduce()
-            packed.buffer /= self.n_workers
-            bits = packed.bits()
+            _sum_all(values, self.n_workers)
+            values /= self.n_workers
+            bits = n_bits(values)
         with self.timer("reduce.combine", verbosity=2):
-            for out, idx, vals in zip(grad_out, picks, packed):
-                out.zero_()
-                out.view(-1)[idx] = vals
+            flat.zero_()
+            flat[index] = values
+            packed.unpack(grad_out)
         return bits
+
+
+    def _pick_all(self, grad_in) -> torch.Tensor:
+        """Positions of every tensor's picks in the flat gradient (tensor after tensor)."""
+        picks, offset = [], 0
+        for t in grad_in:
+            picks.append(self._pick(t, self._budget(t)) + offset)
+            offset += t.nelement()
+        return torch.cat(picks)
 
 
 class _BlockPick:
@@ -568,6 +597,30 @@ class _BlockPick:
         numel = tensor.nelement()
         start = 0 if budget == numel and self._full_block_starts_at_zero else int(self.rng.choice(numel))
         return (torch.arange(budget, device=tensor.device) + start) % numel  # wraps around the end
+
+    _layout_key = None
+
+    def _pick_all(self, grad_in) -> torch.Tensor:
+        """All blocks at once: the start of every block is drawn on the host in tensor order (the
+        same draws as `_pick`), everything else is a handful of element-wise kernels over cached
+        per-pick tables instead of three small kernels per tensor."""
+        numels = [t.nelement() for t in grad_in]
+        budgets = [self._budget(t) for t in grad_in]
+        device = grad_in[0].device
+        key = (tuple(numels), tuple(budgets), device)
+        if key != self._layout_key:
+            count = torch.tensor(budgets, device=device)
+            owner = torch.repeat_interleave(torch.arange(len(grad_in), device=device), count)
+            first = torch.cumsum(count, 0) - count
+            self._within = torch.arange(int(sum(budgets)), device=device) - first[owner]
+            numel_t = torch.tensor(numels, device=device)
+            self._numel_of = numel_t[owner]
+            self._offset_of = (torch.cumsum(numel_t, 0) - numel_t)[owner]
+            self._owner = owner
+            self._layout_key = key
+        starts = [0 if (b == n and self._full_block_starts_at_zero) else int(self.rng.choice(n)) for n, b in zip(numels, budgets)]
+        start_of = torch.tensor(starts, device=device)[self._owner]
+        return (self._within + start_of) % self._numel_of + self._offset_of
 
 
 class _ScatterPick:

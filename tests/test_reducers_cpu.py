@@ -210,3 +210,21 @@ def test_matches_upstream_deterministic_reducers(single_rank_group, monkeypatch)
             assert b1 == b2
             for a, b in zip(gout + mem, gout2 + mem2):
                 assert torch.allclose(a, b, atol=1e-4), (name, step)
+
+
+def test_block_picks_in_one_shot_match_the_per_tensor_definition():
+    """The block-sparse reducers compute all blocks with a few element-wise kernels; positions and
+    the shared random stream must be those of the per-tensor definition (wrapping blocks, the
+    full-tensor case that draws nothing)."""
+    shapes = [(64, 3, 3, 3), (10,), (128, 64), (5, 7), (1,)]
+    for cls, kw in ((R.RandomSparseBlockReducer, dict(rank=2)), (R.UniformRandomSparseBlockReducer, dict(compression=0.3))):
+        a, b = cls(7, "cpu", _timer(), **kw), cls(7, "cpu", _timer(), **kw)
+        tensors = [torch.randn(s) for s in shapes]
+        for step in range(3):
+            got = a._pick_all(tensors)
+            picks, offset = [], 0
+            for t in tensors:
+                picks.append(R._BlockPick._pick(b, t, b._budget(t)) + offset)
+                offset += t.nelement()
+            assert torch.equal(got, torch.cat(picks)), (cls.__name__, step)
+        assert a.rng.randint(1 << 30) == b.rng.randint(1 << 30)   # same number of draws
