@@ -77,6 +77,16 @@ class TensorBuffer:
 
     def all_gather(self, async_op: bool = False):
         world = _dist_world()
+        if world > 1 and not async_op and self.buffer.is_cuda and self.buffer.element_size() == 4:
+            import os
+
+            if os.environ.get("PSGD_B200_COMM", "p2p") == "p2p":
+                from ..ops import native
+
+                if native.use_for_cuda():   # one launch over peer stores instead of the library collective
+                    from ..parallel.symm import native_all_gather
+
+                    return native_all_gather(self.buffer)
         outs: List[torch.Tensor] = [torch.empty_like(self.buffer) for _ in range(world)]
         if world == 1:
             outs[0].copy_(self.buffer)

@@ -423,6 +423,20 @@ def scenario_sparse_reducers_native():
                 assert _same_on_all_ranks(x, world), (name, "outputs differ between ranks")
         assert sparse_combine_status(dev) == 0
         dist.barrier()
+    # ATOMO: native SVD of the narrow matrices, payloads through the in-kernel all-gather of the staging buffer
+    atomo = ours_mod.AtomoReducer(random_seed=5, device=dev, rank=2)
+    small = [(24, 3, 3, 3), (16, 24), (10, 16), (24,)]
+    g = torch.Generator().manual_seed(400 + rank)
+    for step in range(2):
+        grads = [torch.randn(s, generator=g).to(dev) for s in small]
+        outs = [torch.full(s, float("nan"), device=dev) for s in small]
+        mems = [torch.zeros(s, device=dev) for s in small]
+        bits = atomo.reduce(grads, outs, mems)
+        torch.cuda.synchronize()
+        assert bits > 0
+        for x in outs:
+            assert bool(torch.isfinite(x).all()) and _same_on_all_ranks(x, world), "ATOMO outputs differ between ranks"
+    dist.barrier()
     if rank == 0:
         print("SCENARIO-OK")
 
