@@ -127,3 +127,16 @@ def test_multicast_runtime_degrades_without_a_driver():
     state = _McBuffer()
     assert int(lib.psgd_mc_release(ctypes.byref(state))) == 0   # nothing set up: nothing to undo
 
+
+
+def test_in_switch_path_policy(monkeypatch):
+    """`auto` takes the in-switch all-reduce from four workers on unless NCCL_NVLS_ENABLE=0 (how the
+    failure tests run); `nvls` forces it, `bulk` never takes it."""
+    from powersgd_b200.cuda_path import NativeFlatAllReduce
+
+    wants = NativeFlatAllReduce._wants_nvls
+    monkeypatch.delenv("NCCL_NVLS_ENABLE", raising=False)
+    assert not wants("auto", 2) and not wants("auto", 3) and wants("auto", 4) and wants("auto", 8)
+    assert wants("nvls", 2) and not wants("bulk", 8)
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    assert not wants("auto", 8) and wants("nvls", 8)
