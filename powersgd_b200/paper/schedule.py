@@ -317,7 +317,7 @@ def slurm_script(job: Job, output_dir: str, gpus_per_node: int = 8, partition: s
     ])
 
 
-def hyperparameter_record(max_rows: int = 12) -> str:
+def hyperparameter_record(max_rows: int = 1000) -> str:
     """Markdown record of every experiment's jobs and overrides (what the reference keeps as
     config dumps in paper-code/hyperparameters.md), generated from the definitions above:
     `python -m powersgd_b200.paper.schedule > powersgd_b200/paper/HYPERPARAMETERS.md`."""
