@@ -228,3 +228,33 @@ def test_block_picks_in_one_shot_match_the_per_tensor_definition():
                 offset += t.nelement()
             assert torch.equal(got, torch.cat(picks)), (cls.__name__, step)
         assert a.rng.randint(1 << 30) == b.rng.randint(1 << 30)   # same number of draws
+
+
+def test_batched_topk_and_sparse_combine_off_the_gpu():
+    """The CPU formulations behind `topk_abs_many` and `sparse_combine` (what the CUDA kernels are
+    compared with on a GPU): layout of the flat results, memories, rank-order accumulation."""
+    from powersgd_b200.ops.topk import sparse_combine, topk_abs_many
+
+    g = torch.Generator().manual_seed(0)
+    tensors = [torch.randn(6, 5, generator=g), torch.randn(17, generator=g), torch.randn(2, 3, 4, generator=g)]
+    ks = [4, 17, 5]
+    mems = [torch.full_like(t, float("nan")) for t in tensors]
+    values, positions = topk_abs_many(tensors, ks, mems)
+    assert values.shape == (26,) and positions.dtype == torch.int32
+    at = 0
+    for t, k, m in zip(tensors, ks, mems):
+        v, p = values[at : at + k], positions[at : at + k].long()
+        at += k
+        flat = t.reshape(-1)
+        assert torch.equal(v, flat[p]) and p.unique().numel() == k
+        assert torch.equal(v.abs().sort(descending=True).values, torch.topk(flat.abs(), k).values)
+        expect = flat.clone()
+        expect[p] = 0.0
+        assert torch.equal(m.reshape(-1), expect)
+    # three workers, two segments, collisions between workers
+    vals = torch.tensor([[1.0, 2.0, 3.0], [10.0, 20.0, 30.0], [100.0, 200.0, 300.0]])
+    pos = torch.tensor([[0, 3, 1], [3, 0, 1], [2, 3, 0]], dtype=torch.int32)
+    outs = [torch.full((4,), float("nan")), torch.full((2,), float("nan"))]
+    sparse_combine(vals, pos, outs, [2, 3], 3.0)
+    assert torch.allclose(outs[0], torch.tensor([1.0 + 20.0, 0.0, 100.0, 2.0 + 10.0 + 200.0]) / 3.0)
+    assert torch.allclose(outs[1], torch.tensor([300.0, 3.0 + 30.0]) / 3.0)
